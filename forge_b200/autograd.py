@@ -1,0 +1,154 @@
+"""Autograd boundary: a linear whose backward updates its own weight.
+
+Mirror of ``src/fused_grad_optimizer/autograd.py`` (``FusedLinearFunction`` :26-91, ``_apply_fused``
+:94-144, ``_apply_precomputed`` :147-178) with the same argument list and branch table:
+
+    forward   Y = X W^T (+ b)
+    backward  dX = dY W                       enqueued first: it must read the pre-update W
+              then, by case --
+                no config            -> return dW = dY^T X like a plain linear
+                accumulating         -> add dW to the fp32 pending buffer
+                pending accumulation -> dW + pending, optimizer-only kernel
+                use_fused_backward=False -> materialise dW, optimizer-only kernel
+                otherwise            -> fused wgrad + optimizer kernel, dW never exists
+              weight.grad stays None; the bias gradient is returned to autograd.
+
+All optimizer work goes through the C ABI (``forge_b200.kernel``); there is no PyTorch fallback.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from forge_b200 import kernel as K
+from forge_b200.state import FusedOptimizerState, OptimizerConfig  # noqa: F401  (re-exported)
+
+# dX through the library's own GEMM (bf16 CUDA operands); plain `grad_output @ weight` otherwise
+use_forge_dgrad = False
+
+
+def _grad_input(grad_output: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    if (use_forge_dgrad and grad_output.is_cuda and grad_output.dtype == torch.bfloat16
+            and weight.dtype == torch.bfloat16 and weight.stride(1) == 1):
+        go2d = grad_output.reshape(-1, grad_output.shape[-1])
+        if not go2d.is_contiguous():
+            go2d = go2d.contiguous()
+        return K.dgrad(go2d, weight).reshape(*grad_output.shape[:-1], weight.shape[1])
+    return grad_output @ weight
+
+
+class FusedLinearFunction(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, input, weight, bias, optimizer_state, optimizer_config, is_accumulating,
+                l2_manager, use_fused_backward=True):
+        ctx.save_for_backward(input, weight, bias)
+        ctx.optimizer_state = optimizer_state
+        ctx.optimizer_config = optimizer_config
+        ctx.is_accumulating = is_accumulating
+        ctx.l2_manager = l2_manager
+        ctx.use_fused_backward = use_fused_backward
+        return F.linear(input, weight, bias)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, weight, bias = ctx.saved_tensors
+        state, config = ctx.optimizer_state, ctx.optimizer_config
+
+        # before any in-place update of `weight` on this stream
+        grad_input = _grad_input(grad_output, weight) if ctx.needs_input_grad[0] else None
+
+        x2d = input.reshape(-1, input.shape[-1])
+        dy2d = grad_output.reshape(-1, grad_output.shape[-1])
+        grad_weight = None
+        if config is None:
+            grad_weight = dy2d.t() @ x2d
+        elif ctx.is_accumulating:
+            state.accumulate_grad(dy2d.t() @ x2d)
+        else:
+            pending = state.pop_accumulated_grad()
+            if pending is not None:
+                total = (dy2d.t() @ x2d).float()
+                total.add_(pending)
+                _apply_precomputed(total, weight, state, config)
+            elif not ctx.use_fused_backward:
+                _apply_precomputed((dy2d.t() @ x2d).float(), weight, state, config)
+            else:
+                _apply_fused(dy2d, x2d, weight, state, config, ctx.l2_manager)
+
+        grad_bias = dy2d.sum(0) if bias is not None else None
+        return grad_input, grad_weight, grad_bias, None, None, None, None, None
+
+
+def _begin_update(state, config):
+    if config.optimizer_type != state.optimizer_type:
+        raise ValueError(f"config asks for {config.optimizer_type!r} but the state was built for "
+                         f"{state.optimizer_type!r}")
+    state.ensure_buffers()
+    state.increment_step()
+
+
+def _apply_fused(grad_output_2d, input_2d, weight, state, config, l2_manager=None):
+    """Tile-wise fused gradient + optimizer; ``grad_W`` never exists in memory."""
+    _begin_update(state, config)
+    go = grad_output_2d if grad_output_2d.is_contiguous() else grad_output_2d.contiguous()
+    inp = input_2d if input_2d.is_contiguous() else input_2d.contiguous()
+    w = weight.data
+    opt = config.optimizer_type
+    if opt == "sgd":
+        K.fused_grad_sgd(go, inp, w, lr=config.lr, weight_decay=config.weight_decay)
+    elif opt == "sgdm":
+        K.fused_grad_sgd_momentum(go, inp, w, state.m, lr=config.lr, momentum=config.momentum,
+                                  weight_decay=config.weight_decay, nesterov=config.nesterov)
+    elif opt == "lion":
+        K.fused_grad_lion(go, inp, w, state.m, lr=config.lr, beta1=config.beta1, beta2=config.beta2,
+                          weight_decay=config.weight_decay)
+    elif opt == "adamw":
+        kw = dict(lr=config.lr, beta1=config.beta1, beta2=config.beta2, eps=config.eps,
+                  weight_decay=config.weight_decay, step=state.step)
+        if state.state_mode == "int8":
+            K.fused_grad_adamw_int8state(go, inp, w, state.m_q, state.v_q, state.m_scale, state.v_scale,
+                                         qblock=state.qblock_size, **kw)
+        elif state.state_mode == "fp8_block":
+            K.fused_grad_adamw_fp8block(go, inp, w, state.m_q, state.v_q, state.m_scale, state.v_scale,
+                                        qblock=state.qblock_size, **kw)
+        elif state.state_mode == "fp8":
+            state.pre_step_fp8()
+            K.fused_grad_adamw_fp8state(go, inp, w, state, **kw)
+        else:
+            K.fused_grad_adamw(go, inp, w, state.m, state.v, **kw)
+    else:
+        raise ValueError(f"Unknown optimizer: {opt}")
+
+
+def _apply_precomputed(grad_weight, weight, state, config):
+    """Optimizer on a materialised gradient (gradient accumulation, non-fused layers)."""
+    _begin_update(state, config)
+    g = grad_weight if grad_weight.is_contiguous() else grad_weight.contiguous()
+    w = weight.data
+    opt = config.optimizer_type
+    if opt == "sgd":
+        K.optimizer_only_sgd(g, w, lr=config.lr, weight_decay=config.weight_decay)
+    elif opt == "sgdm":
+        K.optimizer_only_sgd_momentum(g, w, state.m, lr=config.lr, momentum=config.momentum,
+                                      weight_decay=config.weight_decay, nesterov=config.nesterov)
+    elif opt == "lion":
+        K.optimizer_only_lion(g, w, state.m, lr=config.lr, beta1=config.beta1, beta2=config.beta2,
+                              weight_decay=config.weight_decay)
+    elif opt == "adamw":
+        kw = dict(lr=config.lr, beta1=config.beta1, beta2=config.beta2, eps=config.eps,
+                  weight_decay=config.weight_decay, step=state.step)
+        if state.state_mode == "int8":
+            K.optimizer_only_adamw_int8state(g, w, state.m_q, state.v_q, state.m_scale, state.v_scale,
+                                             qblock=state.qblock_size, **kw)
+        elif state.state_mode == "fp8_block":
+            K.optimizer_only_adamw_fp8block(g, w, state.m_q, state.v_q, state.m_scale, state.v_scale,
+                                            qblock=state.qblock_size, **kw)
+        elif state.state_mode == "fp8":
+            state.pre_step_fp8()
+            K.optimizer_only_adamw_fp8state(g, w, state, **kw)
+        else:
+            K.optimizer_only_adamw(g, w, state.m, state.v, **kw)
+    else:
+        raise ValueError(f"Unknown optimizer: {opt}")

@@ -1,0 +1,119 @@
+// Per-element optimizer arithmetic shared by the fused wgrad epilogue and the optimizer-only
+// kernels.  Every operation is an explicitly rounded fp32 instruction (no contraction into FMA,
+// IEEE division and square root) in the order of the reference's update
+// (src/fused_grad_optimizer/kernel.py:300-317 AdamW, :203-205 SGD, :424-478 int8 moments,
+// src/fused_grad_optimizer/kernel_fp8_state.py:272-295 fp8 moments), so that a CPU restatement
+// compiled without contraction reproduces the device results bit for bit given the same gradient.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace forge {
+
+enum Optimizer : int { OPT_ADAMW = 0, OPT_SGD = 1, OPT_SGDM = 2, OPT_LION = 3 };
+
+// storage of the optimizer moments
+enum StateMode : int {
+  ST_NONE = 0,        // no moments (plain SGD)
+  ST_F32 = 1,         // fp32 moments
+  ST_BF16 = 2,        // bf16 moments
+  ST_INT8 = 3,        // int8 codes + one fp32 absmax scale per (row, 64 columns)
+  ST_FP8_BLOCK = 4,   // e4m3 codes for m and v + one fp32 absmax scale per (row, 64 columns)
+  ST_FP8_TENSOR = 5   // e4m3 m / e5m2 v + one fp32 scale per tensor (delayed scaling)
+};
+
+enum DType : int { DT_BF16 = 0, DT_F32 = 1 };
+
+// hyper-parameters, narrowed to fp32 on the host exactly as the reference's kernel arguments are
+struct Hyper {
+  float lr;
+  float beta1;
+  float beta2;
+  float eps;
+  float weight_decay;
+  float bc1;             // 1 - beta1^step, evaluated in double on the host then narrowed
+  float bc2;             // 1 - beta2^step
+  float one_m_beta1;     // fp32(1 - beta1), the difference taken in double
+  float one_m_beta2;
+  float decay;           // fp32(1 - lr * weight_decay), evaluated in double
+  float momentum;        // SGD momentum
+  int nesterov;
+};
+
+__device__ __forceinline__ float f_mul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float f_add(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float f_sub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float f_div(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ float f_sqrt(float a) { return __fsqrt_rn(a); }
+
+// AdamW: returns w', updates m and v in place (unrounded fp32 values)
+__device__ __forceinline__ float adamw_update(float w, float g, float& m, float& v, const Hyper& h) {
+  m = f_add(f_mul(h.beta1, m), f_mul(h.one_m_beta1, g));
+  v = f_add(f_mul(h.beta2, v), f_mul(f_mul(h.one_m_beta2, g), g));
+  const float m_hat = f_div(m, h.bc1);
+  const float v_hat = f_div(v, h.bc2);
+  const float w1 = f_mul(w, h.decay);
+  return f_sub(w1, f_div(f_mul(h.lr, m_hat), f_add(f_sqrt(v_hat), h.eps)));
+}
+
+// SGD with decoupled decay: w' = w (1 - lr wd) - lr g
+__device__ __forceinline__ float sgd_update(float w, float g, const Hyper& h) {
+  return f_sub(f_mul(w, h.decay), f_mul(h.lr, g));
+}
+
+// SGD with momentum (buffer semantics of torch.optim.SGD with dampening 0; a zero-initialised
+// buffer gives buf = g on the first step) and the reference's decoupled decay.
+__device__ __forceinline__ float sgdm_update(float w, float g, float& buf, const Hyper& h) {
+  buf = f_add(f_mul(h.momentum, buf), g);
+  const float u = h.nesterov ? f_add(g, f_mul(h.momentum, buf)) : buf;
+  return f_sub(f_mul(w, h.decay), f_mul(h.lr, u));
+}
+
+// Lion: u = sign(beta1 m + (1-beta1) g); w' = w (1 - lr wd) - lr u; m' = beta2 m + (1-beta2) g
+__device__ __forceinline__ float lion_update(float w, float g, float& m, const Hyper& h) {
+  const float c = f_add(f_mul(h.beta1, m), f_mul(h.one_m_beta1, g));
+  const float u = (c > 0.0f) ? 1.0f : ((c < 0.0f) ? -1.0f : 0.0f);
+  m = f_add(f_mul(h.beta2, m), f_mul(h.one_m_beta2, g));
+  return f_sub(f_mul(w, h.decay), f_mul(h.lr, u));
+}
+
+// ----- quantisers -----------------------------------------------------------------------------
+// int8: scale = absmax / 127 + 1e-12 ; code = clamp(rint(x / scale), -127, 127)
+__device__ __forceinline__ float int8_scale(float absmax) {
+  return f_add(f_div(absmax, 127.0f), 1e-12f);
+}
+__device__ __forceinline__ int int8_code(float x, float scale) {
+  const float q = rintf(f_div(x, scale));
+  return static_cast<int>(fminf(fmaxf(q, -127.0f), 127.0f));
+}
+// e4m3 per-block: scale = absmax / 448 + 1e-12 ; code = e4m3_rne(clamp(x / scale, +-448))
+__device__ __forceinline__ float fp8blk_scale(float absmax) {
+  return f_add(f_div(absmax, 448.0f), 1e-12f);
+}
+__device__ __forceinline__ uint8_t e4m3_code(float x_scaled) {
+  const float c = fminf(fmaxf(x_scaled, -448.0f), 448.0f);
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(c, __NV_SATFINITE, __NV_E4M3));
+}
+__device__ __forceinline__ uint8_t e5m2_code(float x_scaled) {
+  const float c = fminf(fmaxf(x_scaled, -57344.0f), 57344.0f);
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(c, __NV_SATFINITE, __NV_E5M2));
+}
+__device__ __forceinline__ float e4m3_to_float(uint8_t c) {
+  const __half_raw hr = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(c), __NV_E4M3);
+  return __half2float(__half(hr));
+}
+__device__ __forceinline__ float e5m2_to_float(uint8_t c) {
+  const __half_raw hr = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(c), __NV_E5M2);
+  return __half2float(__half(hr));
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t b16) {
+  return __uint_as_float(b16 << 16);
+}
+__device__ __forceinline__ uint32_t float_to_bf16_bits(float f) {
+  return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f)));
+}
+
+}  // namespace forge

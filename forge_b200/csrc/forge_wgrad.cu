@@ -1,0 +1,185 @@
+// C-ABI entry of the fused weight-gradient + optimizer update: validation, tensor maps, dispatch.
+#include <algorithm>
+
+#include "forge_host.h"
+#include "forge_wgrad_kernel.cuh"
+
+namespace forge {
+
+// fp32 operands are split into bf16 high and low parts, x = hi + lo with hi = bf16(x) and
+// lo = bf16(x - hi), and the product dY^T X is expanded as hi.hi + hi.lo + lo.hi by stacking three
+// copies along the token axis (rows padded to a multiple of 64 with zeros):
+//   A' = [dY_hi; dY_hi; dY_lo]   B' = [X_hi; X_lo; X_hi]
+// so the same bf16 kernel runs with 3x the reduction length.  The dropped lo.lo term is below
+// 2^-16 relative, i.e. tighter than the TF32 dot the reference uses for fp32 inputs.
+__global__ void split_f32_kernel(const float* __restrict__ src, int64_t rows, int64_t cols, int64_t ld,
+                                 int64_t rows_pad, __nv_bfloat16* __restrict__ dst, int second_is_lo) {
+  const int64_t n = rows_pad * cols;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / cols, c = i % cols;
+    float x = 0.0f;
+    if (r < rows) x = src[r * ld + c];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+    dst[i] = hi;
+    dst[n + i] = second_is_lo ? lo : hi;
+    dst[2 * n + i] = second_is_lo ? hi : lo;
+  }
+}
+
+template <int W_DT, int ST, int OPT>
+static int launch_wgrad(const CUtensorMap& tm_dy, const CUtensorMap& tm_x, const CUtensorMap& tm_w,
+                        const CUtensorMap& tm_m, const CUtensorMap& tm_v, const WgradParams& p, int grid,
+                        cudaStream_t stream) {
+  using Cfg = WgradCfg<W_DT, ST, OPT>;
+  auto kern = forge_wgrad_kernel<W_DT, ST, OPT>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess)
+      return fail(FORGE_ERR_CUDA, "cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
+    attr_set[dev] = true;
+  }
+  kern<<<grid, NUM_THREADS, Cfg::kSmemBytes, stream>>>(tm_dy, tm_x, tm_w, tm_m, tm_v, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "wgrad kernel launch: %s", cudaGetErrorString(e));
+  return FORGE_OK;
+}
+
+template <int W_DT>
+static int dispatch_wgrad(int opt, int st, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& w,
+                          const CUtensorMap& m, const CUtensorMap& v, const WgradParams& p, int grid,
+                          cudaStream_t s) {
+#define FORGE_CASE(OPT_, ST_) \
+  if (opt == OPT_ && st == ST_) return launch_wgrad<W_DT, ST_, OPT_>(a, b, w, m, v, p, grid, s);
+  FORGE_CASE(OPT_ADAMW, ST_BF16)
+  FORGE_CASE(OPT_ADAMW, ST_F32)
+  FORGE_CASE(OPT_ADAMW, ST_INT8)
+  FORGE_CASE(OPT_ADAMW, ST_FP8_BLOCK)
+  FORGE_CASE(OPT_ADAMW, ST_FP8_TENSOR)
+  FORGE_CASE(OPT_SGD, ST_NONE)
+  FORGE_CASE(OPT_SGDM, ST_BF16)
+  FORGE_CASE(OPT_SGDM, ST_F32)
+  FORGE_CASE(OPT_LION, ST_BF16)
+  FORGE_CASE(OPT_LION, ST_F32)
+#undef FORGE_CASE
+  return fail(FORGE_ERR_UNSUPPORTED, "optimizer %d with state mode %d is not built", opt, st);
+}
+
+}  // namespace forge
+
+using namespace forge;
+
+extern "C" size_t forge_wgrad_scratch_bytes(int64_t BT, int64_t V, int64_t H, int32_t operand_dtype) {
+  if (operand_dtype != FORGE_DT_F32 || BT <= 0 || V <= 0 || H <= 0) return 0;
+  const int64_t bt_pad = (BT + 63) / 64 * 64;
+  return static_cast<size_t>(3 * bt_pad) * static_cast<size_t>(V + H) * sizeof(__nv_bfloat16);
+}
+
+extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream) {
+  if (args == nullptr) return fail(FORGE_ERR_INVALID_ARG, "forge_wgrad_update: args is NULL");
+  const ForgeWgradArgs& a = *args;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (a.BT < 0 || a.V < 0 || a.H < 0) return fail(FORGE_ERR_INVALID_ARG, "negative dimension");
+  if (a.V == 0 || a.H == 0) return FORGE_OK;  // empty parameter: nothing to update
+  if (a.W == nullptr) return fail(FORGE_ERR_INVALID_ARG, "W is NULL");
+  if (a.BT > 0 && (a.dY == nullptr || a.X == nullptr)) return fail(FORGE_ERR_INVALID_ARG, "dY or X is NULL");
+  if (a.BT > (1 << 28) || a.V > (1ll << 30) || a.H > (1ll << 30)) return fail(FORGE_ERR_SHAPE, "dimension too large");
+  if (a.w_dtype != FORGE_DT_BF16 && a.w_dtype != FORGE_DT_F32) return fail(FORGE_ERR_INVALID_ARG, "unknown W dtype %d", a.w_dtype);
+  if (a.operand_dtype != FORGE_DT_BF16 && a.operand_dtype != FORGE_DT_F32)
+    return fail(FORGE_ERR_INVALID_ARG, "unknown operand dtype %d", a.operand_dtype);
+  const int opt = a.optimizer;
+  int st = a.state.mode;
+  if (opt < FORGE_OPT_ADAMW || opt > FORGE_OPT_LION) return fail(FORGE_ERR_INVALID_ARG, "unknown optimizer %d", opt);
+  if (opt == FORGE_OPT_SGD) st = FORGE_ST_NONE;
+  if (opt != FORGE_OPT_SGD && (st < FORGE_ST_F32 || st > FORGE_ST_FP8_TENSOR))
+    return fail(FORGE_ERR_INVALID_ARG, "unknown state mode %d", st);
+  if (a.hyper.step < 1 && opt == FORGE_OPT_ADAMW) return fail(FORGE_ERR_INVALID_ARG, "step must be >= 1 (got %d)", a.hyper.step);
+
+  const DeviceInfo* di = current_device_info();
+  if (di == nullptr) return FORGE_ERR_CUDA;
+  if (di->cc_major != 10) return fail(FORGE_ERR_DEVICE, "device has compute capability %d.%d; sm_100 is required", di->cc_major, di->cc_minor);
+
+  const int nm = num_moments(opt);
+  const int ses = state_elem_size(st);
+  const int wes = a.w_dtype == FORGE_DT_BF16 ? 2 : 4;
+  if (nm > 0 && a.state.m == nullptr) return fail(FORGE_ERR_INVALID_ARG, "first moment buffer is NULL");
+  if (nm > 1 && a.state.v == nullptr) return fail(FORGE_ERR_INVALID_ARG, "second moment buffer is NULL");
+  const bool blockq = (st == FORGE_ST_INT8 || st == FORGE_ST_FP8_BLOCK);
+  if (blockq) {
+    if (a.state.qblock != 64) return fail(FORGE_ERR_SHAPE, "qblock must be 64 (got %d)", a.state.qblock);
+    if (a.H % 64 != 0) return fail(FORGE_ERR_SHAPE, "H (%lld) must be divisible by qblock (64)", (long long)a.H);
+    if (a.state.m_scale == nullptr || a.state.v_scale == nullptr) return fail(FORGE_ERR_INVALID_ARG, "scale arrays are NULL");
+    if (a.state.ld_scale < a.H / 64) return fail(FORGE_ERR_INVALID_ARG, "ld_scale too small");
+  }
+  if (st == FORGE_ST_FP8_TENSOR) {
+    if (a.state.m_scale == nullptr || a.state.v_scale == nullptr || a.state.m_absmax_next == nullptr ||
+        a.state.v_absmax_next == nullptr)
+      return fail(FORGE_ERR_INVALID_ARG, "fp8 per-tensor scale / absmax pointers are NULL");
+  }
+
+  // operands: bf16 directly, fp32 through the split into scratch
+  const void* dy = a.dY;
+  const void* x = a.X;
+  int64_t bt = a.BT, ld_dy = a.ld_dy, ld_x = a.ld_x;
+  if (a.BT > 0 && a.operand_dtype == FORGE_DT_F32) {
+    const size_t need = forge_wgrad_scratch_bytes(a.BT, a.V, a.H, FORGE_DT_F32);
+    if (a.scratch == nullptr || a.scratch_bytes < need)
+      return fail(FORGE_ERR_SCRATCH, "fp32 operands need %zu bytes of scratch (got %zu)", need, a.scratch_bytes);
+    if (!aligned16(a.scratch)) return fail(FORGE_ERR_ALIGNMENT, "scratch is not 16-byte aligned");
+    const int64_t bt_pad = (a.BT + 63) / 64 * 64;
+    __nv_bfloat16* sa = static_cast<__nv_bfloat16*>(a.scratch);
+    __nv_bfloat16* sb = sa + 3 * bt_pad * a.V;
+    const int threads = 256;
+    const int blocks_a = static_cast<int>(std::min<int64_t>((bt_pad * a.V + threads - 1) / threads, 148 * 8));
+    const int blocks_b = static_cast<int>(std::min<int64_t>((bt_pad * a.H + threads - 1) / threads, 148 * 8));
+    split_f32_kernel<<<blocks_a, threads, 0, stream>>>(static_cast<const float*>(a.dY), a.BT, a.V, a.ld_dy, bt_pad, sa, 0);
+    split_f32_kernel<<<blocks_b, threads, 0, stream>>>(static_cast<const float*>(a.X), a.BT, a.H, a.ld_x, bt_pad, sb, 1);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "operand split launch: %s", cudaGetErrorString(e));
+    dy = sa; x = sb; bt = 3 * bt_pad; ld_dy = a.V; ld_x = a.H;
+  }
+
+  CUtensorMap tm_dy, tm_x, tm_w, tm_m, tm_v;
+  int rc;
+  if ((rc = encode_tmap_2d(&tm_w, a.W, wes, true, a.V, a.H, a.ld_w, wes == 2 ? 64 : 32, 32, 128)) != FORGE_OK) return rc;
+  if (bt > 0) {
+    if ((rc = encode_tmap_2d(&tm_dy, dy, 2, true, bt, a.V, ld_dy, 64, 64, 128)) != FORGE_OK) return rc;
+    if ((rc = encode_tmap_2d(&tm_x, x, 2, true, bt, a.H, ld_x, 64, 64, 128)) != FORGE_OK) return rc;
+  } else {
+    // no tokens: the kernel treats the accumulator as zero and never touches the operand maps
+    tm_dy = tm_w;
+    tm_x = tm_w;
+  }
+  tm_m = tm_w;
+  tm_v = tm_w;
+  if (nm > 0) {
+    const int box_cols = ses == 4 ? 32 : 64;
+    const int sw = ses == 1 ? 64 : 128;
+    if ((rc = encode_tmap_2d(&tm_m, a.state.m, ses, ses != 1, a.V, a.H, a.state.ld_state, box_cols, 32, sw)) != FORGE_OK) return rc;
+    if (nm > 1 && (rc = encode_tmap_2d(&tm_v, a.state.v, ses, ses != 1, a.V, a.H, a.state.ld_state, box_cols, 32, sw)) != FORGE_OK) return rc;
+  }
+
+  WgradParams p;
+  p.BT = static_cast<int>(bt);
+  p.V = static_cast<int>(a.V);
+  p.H = static_cast<int>(a.H);
+  p.num_kb = static_cast<int>((bt + 63) / 64);
+  p.tiles_m = static_cast<int>((a.V + TILE_M - 1) / TILE_M);
+  p.tiles_n = static_cast<int>((a.H + TILE_N - 1) / TILE_N);
+  p.hyper = make_hyper(a.hyper);
+  p.m_scale = a.state.m_scale;
+  p.v_scale = a.state.v_scale;
+  p.ld_scale = static_cast<int>(a.state.ld_scale);
+  p.m_absmax = a.state.m_absmax_next;
+  p.v_absmax = a.state.v_absmax_next;
+  p.status = a.status;
+  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  const int grid = static_cast<int>(std::min<int64_t>(tiles, di->sm_count));
+
+  if (a.w_dtype == FORGE_DT_BF16) return dispatch_wgrad<DT_BF16>(opt, st, tm_dy, tm_x, tm_w, tm_m, tm_v, p, grid, stream);
+  return dispatch_wgrad<DT_F32>(opt, st, tm_dy, tm_x, tm_w, tm_m, tm_v, p, grid, stream);
+}

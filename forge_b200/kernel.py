@@ -1,0 +1,294 @@
+"""Operator wrappers with the reference's signatures, marshalling tensors into the C ABI.
+
+Mirrors ``src/fused_grad_optimizer/kernel.py:1319-1575`` (``fused_grad_sgd``, ``fused_grad_adamw``,
+``optimizer_only_adamw``, ``fused_grad_adamw_int8state``, ``optimizer_only_adamw_int8state``) and
+``src/fused_grad_optimizer/kernel_fp8_state.py:343-392`` (``fused_grad_adamw_fp8state``).  Shapes:
+``grad_output`` (BT, V), ``input`` (BT, H), ``weight`` and moments (V, H).  Every function updates
+its tensors in place on the current CUDA stream, returns ``None`` and never materialises ``grad_W``.
+
+Additions with no reference counterpart: SGD with momentum, Lion, e4m3 moments with per-block scales.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from forge_b200 import _lib
+from forge_b200._lib import (
+    ForgeHyper, ForgeOptimArgs, ForgeState, ForgeWgradArgs,
+    OPT_ADAMW, OPT_LION, OPT_SGD, OPT_SGDM,
+    ST_FP8_BLOCK, ST_FP8_TENSOR, ST_INT8, ST_NONE,
+)
+
+FP8_E4M3_MAX = 448.0
+FP8_E5M2_MAX = 57344.0
+
+# scratch for fp32 operands, one growing buffer per device (the library itself allocates nothing)
+_scratch: dict[int, torch.Tensor] = {}
+
+
+def _get_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _scratch.get(idx)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _scratch[idx] = buf
+    return buf
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise _lib.ForgeLibraryError(
+                "forge_b200 operators run on CUDA tensors only (sm_100a); there is no CPU path")
+
+
+def _row_major_2d(t: torch.Tensor, what: str):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{what} must be 2-D with a contiguous last dimension (got strides {tuple(t.stride())})")
+
+
+def _hyper(lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1, momentum=0.0, nesterov=False):
+    return ForgeHyper(float(lr), float(beta1), float(beta2), float(eps), float(weight_decay),
+                      float(momentum), int(bool(nesterov)), int(step))
+
+
+def _state(mode=ST_NONE, m=None, v=None, m_scale=None, v_scale=None, m_absmax=None, v_absmax=None, qblock=64):
+    st = ForgeState()
+    st.mode = mode
+    st.qblock = qblock
+    st.m = m.data_ptr() if m is not None else None
+    st.v = v.data_ptr() if v is not None else None
+    st.ld_state = m.stride(0) if m is not None else 0
+    st.m_scale = m_scale.data_ptr() if m_scale is not None else None
+    st.v_scale = v_scale.data_ptr() if v_scale is not None else None
+    st.ld_scale = m_scale.stride(0) if (m_scale is not None and m_scale.dim() == 2) else 0
+    st.m_absmax_next = m_absmax.data_ptr() if m_absmax is not None else None
+    st.v_absmax_next = v_absmax.data_ptr() if v_absmax is not None else None
+    return st
+
+
+def _wgrad(grad_output, input, weight, optimizer, state, hyper):
+    _require_cuda(grad_output, input, weight)
+    assert grad_output.is_contiguous() and input.is_contiguous()
+    _row_major_2d(weight, "weight")
+    BT, V = grad_output.shape
+    H = input.shape[1]
+    if input.shape[0] != BT or tuple(weight.shape) != (V, H):
+        raise ValueError(f"shape mismatch: grad_output {tuple(grad_output.shape)}, input {tuple(input.shape)}, "
+                         f"weight {tuple(weight.shape)}")
+    if grad_output.dtype != input.dtype:
+        raise ValueError("grad_output and input must have the same dtype")
+    lib = _lib.load()
+    a = ForgeWgradArgs()
+    a.dY, a.X, a.W = grad_output.data_ptr(), input.data_ptr(), weight.data_ptr()
+    a.BT, a.V, a.H = BT, V, H
+    a.ld_dy, a.ld_x, a.ld_w = grad_output.stride(0), input.stride(0), weight.stride(0)
+    a.operand_dtype = _lib.dtype_id(grad_output.dtype)
+    a.w_dtype = _lib.dtype_id(weight.dtype)
+    a.optimizer = optimizer
+    a.flags = 0
+    a.state = state
+    a.hyper = hyper
+    nbytes = lib.forge_wgrad_scratch_bytes(BT, V, H, a.operand_dtype)
+    scratch = None
+    if nbytes:
+        scratch = _get_scratch(weight.device, nbytes)
+        a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    a.status = _lib.status_word(weight.device).data_ptr()
+    with torch.cuda.device(weight.device):
+        rc = lib.forge_wgrad_update(ctypes.byref(a), _lib.current_stream_ptr(weight.device))
+    _lib.check(rc, "forge_wgrad_update")
+
+
+def _optim(grad, weight, optimizer, state, hyper):
+    _require_cuda(grad, weight)
+    assert grad.is_contiguous()
+    _row_major_2d(weight, "weight")
+    V, H = weight.shape
+    if tuple(grad.shape) != (V, H):
+        raise ValueError(f"grad shape {tuple(grad.shape)} does not match weight {tuple(weight.shape)}")
+    lib = _lib.load()
+    a = ForgeOptimArgs()
+    a.grad, a.W = grad.data_ptr(), weight.data_ptr()
+    a.V, a.H = V, H
+    a.ld_grad, a.ld_w = grad.stride(0), weight.stride(0)
+    a.grad_dtype = _lib.dtype_id(grad.dtype)
+    a.w_dtype = _lib.dtype_id(weight.dtype)
+    a.optimizer = optimizer
+    a.flags = 0
+    a.state = state
+    a.hyper = hyper
+    with torch.cuda.device(weight.device):
+        rc = lib.forge_optimizer_update(ctypes.byref(a), _lib.current_stream_ptr(weight.device))
+    _lib.check(rc, "forge_optimizer_update")
+
+
+def _moment_state(m, v=None):
+    if m.dtype != (v.dtype if v is not None else m.dtype):
+        raise ValueError("m and v must share a dtype")
+    _row_major_2d(m, "m")
+    if v is not None:
+        _row_major_2d(v, "v")
+        if v.stride(0) != m.stride(0):
+            raise ValueError("m and v must share a row pitch")
+    return _state(_lib.state_mode_id(m.dtype), m, v)
+
+
+# --------------------------------------------------------------------------------------------
+# reference signatures
+# --------------------------------------------------------------------------------------------
+def fused_grad_sgd(grad_output, input, weight, lr: float = 1e-3, weight_decay: float = 0.0):
+    """Fused weight gradient + SGD update (``kernel.py:1319-1339``): ``W = W(1 - lr wd) - lr dW``."""
+    _wgrad(grad_output, input, weight, OPT_SGD, _state(), _hyper(lr, weight_decay=weight_decay))
+
+
+def fused_grad_adamw(grad_output, input, weight, m, v, lr: float = 1e-4, beta1: float = 0.9,
+                     beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.01, step: int = 1):
+    """Fused weight gradient + AdamW update (``kernel.py:1342-1455``); m, v bf16 or fp32, in place."""
+    _require_cuda(m, v)
+    _wgrad(grad_output, input, weight, OPT_ADAMW, _moment_state(m, v),
+           _hyper(lr, beta1, beta2, eps, weight_decay, step))
+
+
+def optimizer_only_adamw(grad, weight, m, v, lr: float = 1e-4, beta1: float = 0.9, beta2: float = 0.999,
+                         eps: float = 1e-8, weight_decay: float = 0.01, step: int = 1):
+    """AdamW on a pre-computed gradient (``kernel.py:1458-1484``)."""
+    _require_cuda(m, v)
+    _optim(grad, weight, OPT_ADAMW, _moment_state(m, v), _hyper(lr, beta1, beta2, eps, weight_decay, step))
+
+
+def _int8_state(weight, m_q, v_q, m_scale, v_scale, qblock, mode=ST_INT8):
+    H = weight.shape[1]
+    assert H % qblock == 0, f"H ({H}) must be divisible by qblock ({qblock})"
+    _require_cuda(m_q, v_q, m_scale, v_scale)
+    _row_major_2d(m_q, "m_q")
+    _row_major_2d(v_q, "v_q")
+    _row_major_2d(m_scale, "m_scale")
+    _row_major_2d(v_scale, "v_scale")
+    if m_q.stride(0) != v_q.stride(0) or m_scale.stride(0) != v_scale.stride(0):
+        raise ValueError("m_q/v_q and m_scale/v_scale must share row pitches")
+    return _state(mode, m_q, v_q, m_scale, v_scale, qblock=qblock)
+
+
+def fused_grad_adamw_int8state(grad_output, input, weight, m_q, v_q, m_scale, v_scale, lr: float = 1e-4,
+                               beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                               weight_decay: float = 0.01, step: int = 1, qblock: int = 64):
+    """Fused weight gradient + AdamW with int8 moments and per-(row, qblock) fp32 absmax scales
+    (``kernel.py:1487-1539``)."""
+    st = _int8_state(weight, m_q, v_q, m_scale, v_scale, qblock)
+    _wgrad(grad_output, input, weight, OPT_ADAMW, st, _hyper(lr, beta1, beta2, eps, weight_decay, step))
+
+
+def optimizer_only_adamw_int8state(grad, weight, m_q, v_q, m_scale, v_scale, lr: float = 1e-4,
+                                   beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                                   weight_decay: float = 0.01, step: int = 1, qblock: int = 64):
+    """AdamW on a pre-computed gradient with int8 moments (``kernel.py:1542-1575``)."""
+    st = _int8_state(weight, m_q, v_q, m_scale, v_scale, qblock)
+    _optim(grad, weight, OPT_ADAMW, st, _hyper(lr, beta1, beta2, eps, weight_decay, step))
+
+
+def _fp8_tensor_state(state):
+    _require_cuda(state.m_fp8, state.v_fp8)
+    return _state(ST_FP8_TENSOR, state.m_fp8, state.v_fp8, state.m_scale, state.v_scale,
+                  state.m_absmax_next, state.v_absmax_next)
+
+
+def fused_grad_adamw_fp8state(grad_output, input, weight, state, lr: float = 1e-4, beta1: float = 0.9,
+                              beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.01,
+                              step: int = 1):
+    """Fused weight gradient + AdamW with e4m3 m / e5m2 v and one delayed scale per tensor
+    (``kernel_fp8_state.py:343-392``).  ``state`` is a ``FusedOptimizerState`` in fp8 mode; the
+    next-step absmax is accumulated by the kernel itself (no scratch arrays, no reduce launches)."""
+    _wgrad(grad_output, input, weight, OPT_ADAMW, _fp8_tensor_state(state),
+           _hyper(lr, beta1, beta2, eps, weight_decay, step))
+
+
+def optimizer_only_adamw_fp8state(grad, weight, state, lr: float = 1e-4, beta1: float = 0.9,
+                                  beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.01,
+                                  step: int = 1):
+    """AdamW on a pre-computed gradient with per-tensor fp8 moments (the reference has no such path:
+    ``autograd.py:158-176`` reaches for ``state.m``, which does not exist in fp8 mode)."""
+    _optim(grad, weight, OPT_ADAMW, _fp8_tensor_state(state), _hyper(lr, beta1, beta2, eps, weight_decay, step))
+
+
+def fp8_prestep(m_scale, v_scale, m_absmax_next, v_absmax_next):
+    """Device-side ``FusedOptimizerState.pre_step_fp8`` (``state.py:132-157``) without host syncs."""
+    _require_cuda(m_scale, v_scale, m_absmax_next, v_absmax_next)
+    lib = _lib.load()
+    with torch.cuda.device(m_scale.device):
+        rc = lib.forge_fp8_prestep(m_scale.data_ptr(), v_scale.data_ptr(), m_absmax_next.data_ptr(),
+                                   v_absmax_next.data_ptr(), _lib.current_stream_ptr(m_scale.device))
+    _lib.check(rc, "forge_fp8_prestep")
+
+
+# --------------------------------------------------------------------------------------------
+# additions without a reference counterpart
+# --------------------------------------------------------------------------------------------
+def fused_grad_adamw_fp8block(grad_output, input, weight, m_q, v_q, m_scale, v_scale, lr: float = 1e-4,
+                              beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                              weight_decay: float = 0.01, step: int = 1, qblock: int = 64):
+    """AdamW with e4m3 codes for both moments and one fp32 absmax scale per (row, 64 columns):
+    the int8 scheme with ``scale = absmax / 448 + 1e-12``.  ``m_q``/``v_q`` are uint8 or float8 views."""
+    st = _int8_state(weight, m_q, v_q, m_scale, v_scale, qblock, mode=ST_FP8_BLOCK)
+    _wgrad(grad_output, input, weight, OPT_ADAMW, st, _hyper(lr, beta1, beta2, eps, weight_decay, step))
+
+
+def optimizer_only_adamw_fp8block(grad, weight, m_q, v_q, m_scale, v_scale, lr: float = 1e-4,
+                                  beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                                  weight_decay: float = 0.01, step: int = 1, qblock: int = 64):
+    st = _int8_state(weight, m_q, v_q, m_scale, v_scale, qblock, mode=ST_FP8_BLOCK)
+    _optim(grad, weight, OPT_ADAMW, st, _hyper(lr, beta1, beta2, eps, weight_decay, step))
+
+
+def fused_grad_sgd_momentum(grad_output, input, weight, buf, lr: float = 1e-3, momentum: float = 0.9,
+                            weight_decay: float = 0.0, nesterov: bool = False):
+    """SGD with momentum: ``buf = mu buf + dW``; ``u = dW + mu buf`` (Nesterov) or ``buf``;
+    ``W = W(1 - lr wd) - lr u``.  Buffer semantics of ``torch.optim.SGD`` with dampening 0."""
+    _require_cuda(buf)
+    _wgrad(grad_output, input, weight, OPT_SGDM, _moment_state(buf),
+           _hyper(lr, weight_decay=weight_decay, momentum=momentum, nesterov=nesterov))
+
+
+def optimizer_only_sgd(grad, weight, lr: float = 1e-3, weight_decay: float = 0.0):
+    _optim(grad, weight, OPT_SGD, _state(), _hyper(lr, weight_decay=weight_decay))
+
+
+def optimizer_only_sgd_momentum(grad, weight, buf, lr: float = 1e-3, momentum: float = 0.9,
+                                weight_decay: float = 0.0, nesterov: bool = False):
+    _require_cuda(buf)
+    _optim(grad, weight, OPT_SGDM, _moment_state(buf),
+           _hyper(lr, weight_decay=weight_decay, momentum=momentum, nesterov=nesterov))
+
+
+def fused_grad_lion(grad_output, input, weight, m, lr: float = 1e-4, beta1: float = 0.9,
+                    beta2: float = 0.99, weight_decay: float = 0.0):
+    """Lion: ``u = sign(b1 m + (1-b1) dW)``; ``W = W(1 - lr wd) - lr u``; ``m = b2 m + (1-b2) dW``."""
+    _require_cuda(m)
+    _wgrad(grad_output, input, weight, OPT_LION, _moment_state(m),
+           _hyper(lr, beta1, beta2, weight_decay=weight_decay))
+
+
+def optimizer_only_lion(grad, weight, m, lr: float = 1e-4, beta1: float = 0.9, beta2: float = 0.99,
+                        weight_decay: float = 0.0):
+    _require_cuda(m)
+    _optim(grad, weight, OPT_LION, _moment_state(m), _hyper(lr, beta1, beta2, weight_decay=weight_decay))
+
+
+def dgrad(grad_output_2d: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``dX = dY @ W`` for bf16 operands through the library's own GEMM (``autograd.py:55``)."""
+    _require_cuda(grad_output_2d, weight)
+    BT, V = grad_output_2d.shape
+    H = weight.shape[1]
+    out = torch.empty(BT, H, dtype=grad_output_2d.dtype, device=grad_output_2d.device)
+    lib = _lib.load()
+    with torch.cuda.device(weight.device):
+        rc = lib.forge_dgrad(grad_output_2d.data_ptr(), weight.data_ptr(), out.data_ptr(), BT, V, H,
+                             grad_output_2d.stride(0), weight.stride(0), out.stride(0),
+                             _lib.status_word(weight.device).data_ptr(), _lib.current_stream_ptr(weight.device))
+    _lib.check(rc, "forge_dgrad")
+    return out

@@ -1,0 +1,204 @@
+"""``FusedLinear`` and ``FusedOptimizerManager`` -- the module-level surface.
+
+Mirror of ``src/fused_grad_optimizer/module.py`` (``FusedLinear`` :35-154, ``FusedOptimizerManager``
+:157-266): same constructor arguments, methods and attributes, so a training loop written for the
+reference runs unchanged:
+
+    model.proj = FusedLinear.from_linear(model.proj, optimizer_type="adamw", state_mode="int8")
+    manager = FusedOptimizerManager(model)
+    other = torch.optim.AdamW(manager.get_non_fused_params(), lr=1e-4)
+    for batch in data:
+        manager.pre_step(lr=lr)
+        model(**batch).loss.backward()      # fused layers update their weights here
+        other.step(); other.zero_grad()
+
+Deliberate differences from the reference:
+* ``pre_step`` builds the step's config with each module's own ``optimizer_type`` and constructor
+  keywords (the reference hard-codes ``"adamw"`` and drops the module's keywords,
+  ``module.py:229``, which breaks SGD modules under a manager).
+* a manager-level ``quantize_state`` override also switches ``state_mode`` (in the reference it only
+  sets ``module.quantize_state``, which ``_ensure_state`` then ignores, ``module.py:189-190,93-96``).
+* ``from_linear`` adopts the source layer's storage without first materialising and initialising a
+  throw-away fp32 weight of the same shape (``module.py:50-51,86``).
+* there is no L2-pinning manager; ``use_l2_pinning`` is accepted and ignored (the kernel keeps the
+  activation panels L2-resident with per-load cache policies instead).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from forge_b200.autograd import FusedLinearFunction
+from forge_b200.state import FusedOptimizerState, OptimizerConfig
+
+
+class FusedLinear(nn.Module):
+    """Drop-in ``nn.Linear`` whose backward computes the weight gradient tile by tile on chip and
+    feeds it straight to the optimizer; the (out_features, in_features) gradient is never allocated."""
+
+    def __init__(self, in_features, out_features, bias=False, optimizer_type="adamw",
+                 quantize_state=False, state_mode=None, _adopt: nn.Linear | None = None,
+                 **optimizer_kwargs):
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        if _adopt is not None:
+            # share the existing parameters' storage (fresh Parameter objects, same data)
+            self.weight = nn.Parameter(_adopt.weight.data, requires_grad=_adopt.weight.requires_grad)
+            self.bias = (nn.Parameter(_adopt.bias.data, requires_grad=_adopt.bias.requires_grad)
+                         if _adopt.bias is not None else None)
+        else:
+            self.weight = nn.Parameter(torch.empty(out_features, in_features))
+            nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
+            if bias:
+                bound = 1 / math.sqrt(in_features) if in_features > 0 else 0
+                self.bias = nn.Parameter(torch.empty(out_features).uniform_(-bound, bound))
+            else:
+                self.bias = None
+        self.optimizer_type = optimizer_type
+        self.quantize_state = quantize_state
+        self.state_mode = state_mode if state_mode is not None else ("int8" if quantize_state else "bf16")
+        self.optimizer_kwargs = optimizer_kwargs
+        self._state: FusedOptimizerState | None = None
+        self._config: OptimizerConfig | None = None
+        self._is_accumulating = False
+        self._l2_manager = None
+        # False: materialise grad_W with a library GEMM and run the optimizer-only kernel
+        self.use_fused_backward = True
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, optimizer_type="adamw", quantize_state=False,
+                    state_mode=None, **optimizer_kwargs):
+        """Create from an existing ``nn.Linear``, sharing its weight (and bias) storage."""
+        return cls(linear.in_features, linear.out_features, bias=linear.bias is not None,
+                   optimizer_type=optimizer_type, quantize_state=quantize_state,
+                   state_mode=state_mode, _adopt=linear, **optimizer_kwargs)
+
+    def _ensure_state(self):
+        if self._state is None:
+            self._state = FusedOptimizerState(self.weight, self.optimizer_type,
+                                              quantize_state=self.quantize_state,
+                                              state_mode=self.state_mode)
+
+    def update_optimizer_config(self, config=None, **kwargs):
+        """Set the hyper-parameters of the coming step: a shared ``OptimizerConfig`` or keywords
+        merged over the constructor's ``optimizer_kwargs``."""
+        if config is not None:
+            self._config = config
+        else:
+            self._config = OptimizerConfig(optimizer_type=self.optimizer_type,
+                                           **{**self.optimizer_kwargs, **kwargs})
+
+    def set_accumulating(self, is_accumulating: bool):
+        self._is_accumulating = is_accumulating
+
+    def set_l2_manager(self, l2_manager):
+        self._l2_manager = l2_manager
+
+    def forward(self, x):
+        if not self.training:
+            return F.linear(x, self.weight, self.bias)
+        self._ensure_state()
+        return FusedLinearFunction.apply(x, self.weight, self.bias, self._state, self._config,
+                                         self._is_accumulating, self._l2_manager,
+                                         self.use_fused_backward)
+
+    def get_optimizer_state_dict(self):
+        return None if self._state is None else self._state.state_dict()
+
+    def load_optimizer_state_dict(self, d):
+        self._ensure_state()
+        self._state.load_state_dict(d)
+
+    def extra_repr(self):
+        s = (f"in_features={self.in_features}, out_features={self.out_features}, "
+             f"bias={self.bias is not None}, optimizer={self.optimizer_type}")
+        if self.state_mode != "bf16":
+            s += f", state_mode={self.state_mode}"
+        return s
+
+
+class FusedOptimizerManager:
+    """Coordinates every ``FusedLinear`` of a model: per-step configs, accumulation phase, the list
+    of parameters left to the user's own optimizer, and checkpointing of the fused state."""
+
+    def __init__(self, model: nn.Module, gradient_accumulation_steps: int = 1,
+                 use_l2_pinning: bool = False, quantize_state: bool | None = None):
+        self.model = model
+        self.gradient_accumulation_steps = gradient_accumulation_steps
+        self._global_step = 0
+        self._micro_step = 0
+        self._l2_manager = None  # accepted for signature compatibility; see the module docstring
+        self._fused_modules: list[FusedLinear] = []
+        self._fused_module_names: dict[int, str] = {}
+        self._fused_param_ids: set[int] = set()
+        for name, module in model.named_modules():
+            if not isinstance(module, FusedLinear):
+                continue
+            if quantize_state is not None and module._state is None:
+                module.quantize_state = quantize_state
+                module.state_mode = "int8" if quantize_state else "bf16"
+            self._fused_modules.append(module)
+            self._fused_module_names[id(module)] = name
+            # only the weight is fused; a bias keeps flowing through autograd to the user's optimizer
+            self._fused_param_ids.add(id(module.weight))
+
+    def get_non_fused_params(self) -> list[nn.Parameter]:
+        """Parameters NOT updated by the fused kernels -- hand these to your own optimizer."""
+        return [p for p in self.model.parameters()
+                if p.requires_grad and id(p) not in self._fused_param_ids]
+
+    def pre_step(self, lr: float | None = None, step: int | None = None,
+                 is_accumulating: bool | None = None, **kwargs):
+        """Call before each forward pass.  ``step`` is accepted for compatibility; the bias
+        correction uses each parameter's own update count, as in the reference."""
+        self._micro_step += 1
+        if is_accumulating is None:
+            is_accumulating = (self._micro_step % self.gradient_accumulation_steps) != 0
+        if not is_accumulating:
+            self._global_step += 1
+        if lr is None:
+            lr = 1e-4
+        # one shared config per distinct (optimizer, constructor keywords) instead of one per module
+        configs: dict[tuple, OptimizerConfig] = {}
+        for m in self._fused_modules:
+            key = (m.optimizer_type, tuple(sorted(m.optimizer_kwargs.items())))
+            cfg = configs.get(key)
+            if cfg is None:
+                cfg = OptimizerConfig(optimizer_type=m.optimizer_type,
+                                      **{**m.optimizer_kwargs, **kwargs, "lr": lr})
+                configs[key] = cfg
+            m._config = cfg
+            m._is_accumulating = is_accumulating
+
+    def optimizer_state_dict(self) -> dict:
+        modules = {}
+        for m in self._fused_modules:
+            sd = m.get_optimizer_state_dict()
+            if sd is not None:
+                modules[self._fused_module_names[id(m)]] = sd
+        return {"global_step": self._global_step, "micro_step": self._micro_step, "modules": modules}
+
+    def load_optimizer_state_dict(self, state: dict):
+        self._global_step = state["global_step"]
+        self._micro_step = state["micro_step"]
+        for m in self._fused_modules:
+            sd = state["modules"].get(self._fused_module_names[id(m)])
+            if sd is not None:
+                m.load_optimizer_state_dict(sd)
+
+    @property
+    def l2_manager(self):
+        return self._l2_manager
+
+    @property
+    def num_fused_params(self) -> int:
+        return len(self._fused_param_ids)
+
+    @property
+    def num_fused_modules(self) -> int:
+        return len(self._fused_modules)

@@ -1,0 +1,167 @@
+/* forge_b200 -- C ABI of the B200 (sm_100a) fused weight-gradient + optimizer path.
+ *
+ * Plain C types only: device pointers, sizes, enums as int, hyper-parameters as float/double and a
+ * CUDA stream passed as void*.  Every function returns FORGE_OK (0) or a negative FORGE_ERR_* code;
+ * forge_last_error_string() gives the message of the last failure on the calling thread.  The
+ * library allocates no device memory; every buffer belongs to the caller.  All launches go to the
+ * stream the caller passes and return without synchronising.
+ *
+ * Shapes follow the reference: dY is (BT, V) "grad_output", X is (BT, H) "input", W and the
+ * optimizer moments are (V, H); all row-major with the last dimension contiguous.
+ */
+#ifndef FORGE_B200_H_
+#define FORGE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FORGE_ABI_VERSION 1
+
+/* error codes */
+#define FORGE_OK 0
+#define FORGE_ERR_INVALID_ARG (-1)  /* null pointer, unknown enum, negative size                  */
+#define FORGE_ERR_ALIGNMENT (-2)    /* pointer not 16-byte aligned or row pitch not 16-byte sized */
+#define FORGE_ERR_SHAPE (-3)        /* shape not supported (e.g. H % 64 != 0 with int8 moments)    */
+#define FORGE_ERR_UNSUPPORTED (-4)  /* dtype / optimizer / state-mode combination not built        */
+#define FORGE_ERR_CUDA (-5)         /* a CUDA runtime or driver call failed                        */
+#define FORGE_ERR_DEVICE (-6)       /* device is not sm_100                                        */
+#define FORGE_ERR_TIMEOUT (-7)      /* a kernel abandoned a bounded wait (see forge_read_status)   */
+#define FORGE_ERR_SCRATCH (-8)      /* scratch buffer missing or too small                         */
+
+/* element types of dY/X and of W */
+#define FORGE_DT_BF16 0
+#define FORGE_DT_F32 1
+
+/* optimizers */
+#define FORGE_OPT_ADAMW 0
+#define FORGE_OPT_SGD 1   /* plain SGD with decoupled decay, no state                       */
+#define FORGE_OPT_SGDM 2  /* SGD with momentum (one moment buffer), optional Nesterov       */
+#define FORGE_OPT_LION 3  /* Lion (one moment buffer)                                       */
+
+/* storage of the optimizer moments */
+#define FORGE_ST_NONE 0
+#define FORGE_ST_F32 1
+#define FORGE_ST_BF16 2
+#define FORGE_ST_INT8 3       /* int8 codes + fp32 absmax scale per (row, 64 columns)            */
+#define FORGE_ST_FP8_BLOCK 4  /* e4m3 codes (m and v) + fp32 absmax scale per (row, 64 columns)  */
+#define FORGE_ST_FP8_TENSOR 5 /* e4m3 m, e5m2 v, one fp32 scale per tensor, delayed scaling      */
+
+/* flags */
+#define FORGE_FLAG_NONE 0u
+
+/* Hyper-parameters of one update.  `step` is the 1-based count of updates of this parameter; the
+ * bias corrections 1 - beta^step are evaluated in double and narrowed to float, as the reference
+ * does (src/fused_grad_optimizer/kernel.py:1367-1368). */
+typedef struct ForgeHyper {
+  double lr;
+  double beta1;
+  double beta2;
+  double eps;
+  double weight_decay;
+  double momentum; /* FORGE_OPT_SGDM only */
+  int32_t nesterov;
+  int32_t step;
+} ForgeHyper;
+
+/* The optimizer state of one (V, H) parameter.  Unused pointers are NULL. */
+typedef struct ForgeState {
+  int32_t mode;      /* FORGE_ST_*                                                             */
+  int32_t qblock;    /* columns per quantisation block; must be 64 for INT8 / FP8_BLOCK         */
+  void* m;           /* first moment / momentum buffer, (V, H), element type by `mode`          */
+  void* v;           /* second moment, (V, H)                                                   */
+  int64_t ld_state;  /* row pitch of m and v in elements                                        */
+  float* m_scale;    /* INT8 / FP8_BLOCK: (V, H/qblock) fp32; FP8_TENSOR: one fp32 scalar       */
+  float* v_scale;
+  int64_t ld_scale;  /* row pitch of the scale arrays in floats (INT8 / FP8_BLOCK)              */
+  float* m_absmax_next; /* FP8_TENSOR: running max |m'| of this step (atomic max), one scalar   */
+  float* v_absmax_next;
+} ForgeState;
+
+/* Arguments of the fused weight-gradient + optimizer update. */
+typedef struct ForgeWgradArgs {
+  const void* dY;    /* (BT, V) row-major                                                       */
+  const void* X;     /* (BT, H) row-major                                                       */
+  void* W;           /* (V, H) row-major, updated in place                                      */
+  int64_t BT, V, H;
+  int64_t ld_dy, ld_x, ld_w; /* row pitches in elements                                         */
+  int32_t operand_dtype;     /* FORGE_DT_* of dY and X                                          */
+  int32_t w_dtype;           /* FORGE_DT_* of W                                                 */
+  int32_t optimizer;         /* FORGE_OPT_*                                                     */
+  uint32_t flags;
+  ForgeState state;
+  ForgeHyper hyper;
+  void* scratch;             /* only for fp32 operands: see forge_wgrad_scratch_bytes           */
+  size_t scratch_bytes;
+  int32_t* status;           /* optional device word; a kernel that abandons a wait writes its
+                                code here (0 = ok); see forge_read_status                       */
+} ForgeWgradArgs;
+
+/* Fused dW = dY^T X and in-place optimizer update of W and its moments; no gradient tensor is
+ * written to memory.  Replaces the reference's fused_grad_adamw / fused_grad_sgd /
+ * fused_grad_adamw_int8state / fused_grad_adamw_fp8state
+ * (src/fused_grad_optimizer/kernel.py:1342-1455, :1319-1339, :1487-1539;
+ * src/fused_grad_optimizer/kernel_fp8_state.py:343-392).  Must be enqueued after the dX GEMM that
+ * reads the same W on the same stream (src/fused_grad_optimizer/autograd.py:50-55). */
+int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream);
+
+/* Bytes of scratch forge_wgrad_update needs for the given operand type (0 for bf16 operands; fp32
+ * operands are split into bf16 high/low parts in scratch before the GEMM). */
+size_t forge_wgrad_scratch_bytes(int64_t BT, int64_t V, int64_t H, int32_t operand_dtype);
+
+/* Arguments of the optimizer-only update on a materialised gradient. */
+typedef struct ForgeOptimArgs {
+  const void* grad;  /* (V, H) row-major gradient                                                */
+  void* W;           /* (V, H) row-major, updated in place                                       */
+  int64_t V, H;
+  int64_t ld_grad, ld_w;
+  int32_t grad_dtype; /* FORGE_DT_*                                                              */
+  int32_t w_dtype;
+  int32_t optimizer;
+  uint32_t flags;
+  ForgeState state;
+  ForgeHyper hyper;
+} ForgeOptimArgs;
+
+/* Optimizer update from a gradient that already exists in memory (gradient accumulation, layers
+ * that opt out of the fused backward).  Replaces optimizer_only_adamw /
+ * optimizer_only_adamw_int8state (src/fused_grad_optimizer/kernel.py:1458-1484, :1542-1575) and the
+ * SGD branch of _apply_precomputed (src/fused_grad_optimizer/autograd.py:153-156).  Shares the
+ * per-element arithmetic of forge_wgrad_update bit for bit. */
+int forge_optimizer_update(const ForgeOptimArgs* args, void* cuda_stream);
+
+/* Delayed-scaling bookkeeping of FORGE_ST_FP8_TENSOR before an update, on the device and without a
+ * host synchronisation: scale <- clamp(absmax_next, 1e-8) / MAX, capped at twice the previous scale
+ * when that is positive; absmax_next <- 0.  Replaces FusedOptimizerState.pre_step_fp8
+ * (src/fused_grad_optimizer/state.py:132-157), which reads both scales back to the host. */
+int forge_fp8_prestep(float* m_scale, float* v_scale, float* m_absmax_next, float* v_absmax_next,
+                      void* cuda_stream);
+
+/* dX = dY W : (BT, V) x (V, H) -> (BT, H), bf16 in, fp32 accumulate, bf16 out.  Replaces
+ * `grad_input = grad_output @ weight` (src/fused_grad_optimizer/autograd.py:55). */
+int forge_dgrad(const void* dY, const void* W, void* dX, int64_t BT, int64_t V, int64_t H,
+                int64_t ld_dy, int64_t ld_w, int64_t ld_dx, int32_t* status, void* cuda_stream);
+
+/* Bytes of optimizer state the allocator must provide for a (V, H) parameter: the moment arrays
+ * and, separately, the scale arrays (src/fused_grad_optimizer/state.py:95-130). */
+int forge_state_bytes(int32_t optimizer, int32_t mode, int64_t V, int64_t H, int32_t qblock,
+                      size_t* moment_bytes_each, size_t* scale_bytes_each, int32_t* num_moments);
+
+/* Copies the device status word to the host after synchronising the stream and clears it.
+ * Returns FORGE_OK, or FORGE_ERR_TIMEOUT with the kernel's code in *code_out. */
+int forge_read_status(int32_t* status, int32_t* code_out, void* cuda_stream);
+
+/* Message of the last error on the calling thread (never NULL). */
+const char* forge_last_error_string(void);
+
+/* FORGE_ABI_VERSION the library was built with. */
+int forge_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FORGE_B200_H_ */
