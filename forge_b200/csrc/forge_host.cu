@@ -93,9 +93,16 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, bool is_f
                                 : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
                                 : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
                                                       : CU_TENSOR_MAP_SWIZZLE_NONE;
-  const CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // a thread that has made no runtime call yet (e.g. an autograd worker) has no context bound:
+    // bind the primary context of the current device and try once more
+    cudaFree(nullptr);
+    r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS)
     return fail(FORGE_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld cols=%lld ld=%lld)",
                 static_cast<int>(r), (long long)rows, (long long)cols, (long long)ld);
@@ -117,6 +124,8 @@ Hyper make_hyper(const ForgeHyper& h) {
   o.one_m_beta1 = static_cast<float>(1.0 - h.beta1);
   o.one_m_beta2 = static_cast<float>(1.0 - h.beta2);
   o.decay = static_cast<float>(1.0 - h.lr * h.weight_decay);
+  o.lr_over_bc1 = static_cast<float>(static_cast<double>(o.lr) / static_cast<double>(o.bc1));
+  o.inv_bc2 = static_cast<float>(1.0 / static_cast<double>(o.bc2));
   o.momentum = static_cast<float>(h.momentum);
   o.nesterov = h.nesterov;
   return o;

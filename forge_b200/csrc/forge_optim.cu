@@ -166,15 +166,16 @@ __global__ void __launch_bounds__(256) forge_optim_kernel(const OptimParams p) {
         av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 2));
         const float sm_new = (ST == ST_INT8) ? int8_scale(am) : fp8blk_scale(am);
         const float sv_new = (ST == ST_INT8) ? int8_scale(av) : fp8blk_scale(av);
+          const float rsm = f_div(1.0f, sm_new), rsv = f_div(1.0f, sv_new);
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
           uint32_t mc, vc;
           if constexpr (ST == ST_INT8) {
-            mc = static_cast<uint32_t>(int8_code(m[k], sm_new)) & 0xFFu;
-            vc = static_cast<uint32_t>(int8_code(v[k], sv_new)) & 0xFFu;
+            mc = static_cast<uint32_t>(int8_code(m[k], sm_new, rsm)) & 0xFFu;
+            vc = static_cast<uint32_t>(int8_code(v[k], sv_new, rsv)) & 0xFFu;
           } else {
-            mc = e4m3_code(f_div(m[k], sm_new));
-            vc = e4m3_code(f_div(v[k], sv_new));
+            mc = e4m3_code(div_by_rcp(m[k], sm_new, rsm));
+            vc = e4m3_code(div_by_rcp(v[k], sv_new, rsv));
           }
           mo[k >> 2] |= mc << (8 * (k & 3));
           vo[k >> 2] |= vc << (8 * (k & 3));

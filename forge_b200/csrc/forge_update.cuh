@@ -1,9 +1,17 @@
 // Per-element optimizer arithmetic shared by the fused wgrad epilogue and the optimizer-only
-// kernels.  Every operation is an explicitly rounded fp32 instruction (no contraction into FMA,
-// IEEE division and square root) in the order of the reference's update
-// (src/fused_grad_optimizer/kernel.py:300-317 AdamW, :203-205 SGD, :424-478 int8 moments,
-// src/fused_grad_optimizer/kernel_fp8_state.py:272-295 fp8 moments), so that a CPU restatement
-// compiled without contraction reproduces the device results bit for bit given the same gradient.
+// kernels, following the reference's update (src/fused_grad_optimizer/kernel.py:300-317 AdamW,
+// :203-205 SGD, :424-478 int8 moments, src/fused_grad_optimizer/kernel_fp8_state.py:272-295 fp8
+// moments).
+//
+// What is reproduced bit for bit (given the same fp32 gradient) by a CPU restatement compiled
+// without contraction: the new moments m', v' (explicitly rounded multiplies and adds in the
+// reference's order), the int8 / fp8 codes and their scales (correctly rounded quotients), and the
+// SGD / momentum / Lion weights (multiplies and adds only).
+// What is NOT bit-reproduced: the AdamW weight.  Its bias-corrected quotient lr*m_hat/(sqrt(v_hat)
+// + eps) is evaluated with the hardware's approximate reciprocal and square root and folded
+// constants (relative error ~1e-6 of an update that is itself ~1e-3 of W), which keeps the stored
+// weight within one bf16 ULP of the IEEE evaluation and removes three IEEE divisions and a square
+// root from every element of an epilogue that otherwise could not keep up with HBM.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -40,6 +48,8 @@ struct Hyper {
   float decay;           // fp32(1 - lr * weight_decay), evaluated in double
   float momentum;        // SGD momentum
   int nesterov;
+  float lr_over_bc1;     // fp32(lr / bc1), quotient taken in double
+  float inv_bc2;         // fp32(1 / bc2)
 };
 
 __device__ __forceinline__ float f_mul(float a, float b) { return __fmul_rn(a, b); }
@@ -48,14 +58,32 @@ __device__ __forceinline__ float f_sub(float a, float b) { return __fsub_rn(a, b
 __device__ __forceinline__ float f_div(float a, float b) { return __fdiv_rn(a, b); }
 __device__ __forceinline__ float f_sqrt(float a) { return __fsqrt_rn(a); }
 
-// AdamW: returns w', updates m and v in place (unrounded fp32 values)
+__device__ __forceinline__ float sqrt_approx(float x) {
+  float y;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Correctly rounded a / b given rb = RN(1 / b): one multiply and two fused corrections (Markstein).
+// Valid while no intermediate underflows, which holds for the quantiser's operands.
+__device__ __forceinline__ float div_by_rcp(float a, float b, float rb) {
+  const float q = __fmul_rn(a, rb);
+  const float r = __fmaf_rn(-q, b, a);
+  return __fmaf_rn(r, rb, q);
+}
+
+// AdamW: returns w', updates m and v in place (unrounded fp32 values, bit-reproducible)
 __device__ __forceinline__ float adamw_update(float w, float g, float& m, float& v, const Hyper& h) {
   m = f_add(f_mul(h.beta1, m), f_mul(h.one_m_beta1, g));
   v = f_add(f_mul(h.beta2, v), f_mul(f_mul(h.one_m_beta2, g), g));
-  const float m_hat = f_div(m, h.bc1);
-  const float v_hat = f_div(v, h.bc2);
-  const float w1 = f_mul(w, h.decay);
-  return f_sub(w1, f_div(f_mul(h.lr, m_hat), f_add(f_sqrt(v_hat), h.eps)));
+  const float den = sqrt_approx(v * h.inv_bc2) + h.eps;
+  const float q = (m * h.lr_over_bc1) * rcp_approx(den);
+  return __fmaf_rn(w, h.decay, -q);
 }
 
 // SGD with decoupled decay: w' = w (1 - lr wd) - lr g
@@ -84,8 +112,9 @@ __device__ __forceinline__ float lion_update(float w, float g, float& m, const H
 __device__ __forceinline__ float int8_scale(float absmax) {
   return f_add(f_div(absmax, 127.0f), 1e-12f);
 }
-__device__ __forceinline__ int int8_code(float x, float scale) {
-  const float q = rintf(f_div(x, scale));
+// `rscale` = RN(1 / scale), computed once per block with the IEEE reciprocal
+__device__ __forceinline__ int int8_code(float x, float scale, float rscale) {
+  const float q = rintf(div_by_rcp(x, scale, rscale));
   return static_cast<int>(fminf(fmaxf(q, -127.0f), 127.0f));
 }
 // e4m3 per-block: scale = absmax / 448 + 1e-12 ; code = e4m3_rne(clamp(x / scale, +-448))

@@ -1,4 +1,6 @@
 // C-ABI entry of the fused weight-gradient + optimizer update: validation, tensor maps, dispatch.
+#include <string.h>
+
 #include <algorithm>
 
 #include "forge_host.h"
@@ -28,11 +30,38 @@ __global__ void split_f32_kernel(const float* __restrict__ src, int64_t rows, in
   }
 }
 
+// what the launcher needs to build the W / moment tensor maps for a given kernel configuration
+struct StateTensors {
+  void* W;
+  void* m;
+  void* v;
+  int64_t V, H, ld_w, ld_state;
+};
+
 template <int W_DT, int ST, int OPT>
-static int launch_wgrad(const CUtensorMap& tm_dy, const CUtensorMap& tm_x, const CUtensorMap& tm_w,
-                        const CUtensorMap& tm_m, const CUtensorMap& tm_v, const WgradParams& p, int grid,
-                        cudaStream_t stream) {
+static int launch_wgrad(const CUtensorMap& tm_dy, const CUtensorMap& tm_x, const StateTensors& t,
+                        const WgradParams& p, int grid, cudaStream_t stream) {
   using Cfg = WgradCfg<W_DT, ST, OPT>;
+  // per-warp boxes: 32 rows x (one swizzle row of the chunk)
+  CUtensorMap tm_w, tm_m, tm_v;
+  int rc;
+  using WG = BoxGeom<Cfg::kWRB>;
+  if ((rc = encode_tmap_2d(&tm_w, t.W, Cfg::kWES, true, t.V, t.H, t.ld_w, WG::kBoxRowBytes / Cfg::kWES, 32,
+                           WG::kSwizzle)) != FORGE_OK)
+    return rc;
+  tm_m = tm_w;
+  tm_v = tm_w;
+  if constexpr (Cfg::kNMom > 0) {
+    using SG = BoxGeom<Cfg::kSRB>;
+    if ((rc = encode_tmap_2d(&tm_m, t.m, Cfg::kSES, Cfg::kSES != 1, t.V, t.H, t.ld_state,
+                             SG::kBoxRowBytes / Cfg::kSES, 32, SG::kSwizzle)) != FORGE_OK)
+      return rc;
+    if constexpr (Cfg::kNMom > 1) {
+      if ((rc = encode_tmap_2d(&tm_v, t.v, Cfg::kSES, Cfg::kSES != 1, t.V, t.H, t.ld_state,
+                               SG::kBoxRowBytes / Cfg::kSES, 32, SG::kSwizzle)) != FORGE_OK)
+        return rc;
+    }
+  }
   auto kern = forge_wgrad_kernel<W_DT, ST, OPT>;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -43,18 +72,19 @@ static int launch_wgrad(const CUtensorMap& tm_dy, const CUtensorMap& tm_x, const
       return fail(FORGE_ERR_CUDA, "cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
     attr_set[dev] = true;
   }
-  kern<<<grid, NUM_THREADS, Cfg::kSmemBytes, stream>>>(tm_dy, tm_x, tm_w, tm_m, tm_v, p);
+  // with no tokens the operand maps are never used; pass valid ones anyway
+  kern<<<grid, NUM_THREADS, Cfg::kSmemBytes, stream>>>(p.num_kb > 0 ? tm_dy : tm_w, p.num_kb > 0 ? tm_x : tm_w,
+                                                       tm_w, tm_m, tm_v, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "wgrad kernel launch: %s", cudaGetErrorString(e));
   return FORGE_OK;
 }
 
 template <int W_DT>
-static int dispatch_wgrad(int opt, int st, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& w,
-                          const CUtensorMap& m, const CUtensorMap& v, const WgradParams& p, int grid,
-                          cudaStream_t s) {
+static int dispatch_wgrad(int opt, int st, const CUtensorMap& a, const CUtensorMap& b, const StateTensors& t,
+                          const WgradParams& p, int grid, cudaStream_t s) {
 #define FORGE_CASE(OPT_, ST_) \
-  if (opt == OPT_ && st == ST_) return launch_wgrad<W_DT, ST_, OPT_>(a, b, w, m, v, p, grid, s);
+  if (opt == OPT_ && st == ST_) return launch_wgrad<W_DT, ST_, OPT_>(a, b, t, p, grid, s);
   FORGE_CASE(OPT_ADAMW, ST_BF16)
   FORGE_CASE(OPT_ADAMW, ST_F32)
   FORGE_CASE(OPT_ADAMW, ST_INT8)
@@ -104,8 +134,6 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
   if (di->cc_major != 10) return fail(FORGE_ERR_DEVICE, "device has compute capability %d.%d; sm_100 is required", di->cc_major, di->cc_minor);
 
   const int nm = num_moments(opt);
-  const int ses = state_elem_size(st);
-  const int wes = a.w_dtype == FORGE_DT_BF16 ? 2 : 4;
   if (nm > 0 && a.state.m == nullptr) return fail(FORGE_ERR_INVALID_ARG, "first moment buffer is NULL");
   if (nm > 1 && a.state.v == nullptr) return fail(FORGE_ERR_INVALID_ARG, "second moment buffer is NULL");
   const bool blockq = (st == FORGE_ST_INT8 || st == FORGE_ST_FP8_BLOCK);
@@ -143,31 +171,23 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
     dy = sa; x = sb; bt = 3 * bt_pad; ld_dy = a.V; ld_x = a.H;
   }
 
-  CUtensorMap tm_dy, tm_x, tm_w, tm_m, tm_v;
+  CUtensorMap tm_dy, tm_x;
   int rc;
-  if ((rc = encode_tmap_2d(&tm_w, a.W, wes, true, a.V, a.H, a.ld_w, wes == 2 ? 64 : 32, 32, 128)) != FORGE_OK) return rc;
+  memset(&tm_dy, 0, sizeof(tm_dy));
+  memset(&tm_x, 0, sizeof(tm_x));
   if (bt > 0) {
-    if ((rc = encode_tmap_2d(&tm_dy, dy, 2, true, bt, a.V, ld_dy, 64, 64, 128)) != FORGE_OK) return rc;
-    if ((rc = encode_tmap_2d(&tm_x, x, 2, true, bt, a.H, ld_x, 64, 64, 128)) != FORGE_OK) return rc;
-  } else {
-    // no tokens: the kernel treats the accumulator as zero and never touches the operand maps
-    tm_dy = tm_w;
-    tm_x = tm_w;
+    if ((rc = encode_tmap_2d(&tm_dy, dy, 2, true, bt, a.V, ld_dy, 64, OP_BK, 128)) != FORGE_OK) return rc;
+    if ((rc = encode_tmap_2d(&tm_x, x, 2, true, bt, a.H, ld_x, 64, OP_BK, 128)) != FORGE_OK) return rc;
   }
-  tm_m = tm_w;
-  tm_v = tm_w;
-  if (nm > 0) {
-    const int box_cols = ses == 4 ? 32 : 64;
-    const int sw = ses == 1 ? 64 : 128;
-    if ((rc = encode_tmap_2d(&tm_m, a.state.m, ses, ses != 1, a.V, a.H, a.state.ld_state, box_cols, 32, sw)) != FORGE_OK) return rc;
-    if (nm > 1 && (rc = encode_tmap_2d(&tm_v, a.state.v, ses, ses != 1, a.V, a.H, a.state.ld_state, box_cols, 32, sw)) != FORGE_OK) return rc;
-  }
+  StateTensors t;
+  t.W = a.W; t.m = a.state.m; t.v = a.state.v;
+  t.V = a.V; t.H = a.H; t.ld_w = a.ld_w; t.ld_state = a.state.ld_state;
 
   WgradParams p;
   p.BT = static_cast<int>(bt);
   p.V = static_cast<int>(a.V);
   p.H = static_cast<int>(a.H);
-  p.num_kb = static_cast<int>((bt + 63) / 64);
+  p.num_kb = static_cast<int>((bt + OP_BK - 1) / OP_BK);
   p.tiles_m = static_cast<int>((a.V + TILE_M - 1) / TILE_M);
   p.tiles_n = static_cast<int>((a.H + TILE_N - 1) / TILE_N);
   p.hyper = make_hyper(a.hyper);
@@ -180,6 +200,6 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   const int grid = static_cast<int>(std::min<int64_t>(tiles, di->sm_count));
 
-  if (a.w_dtype == FORGE_DT_BF16) return dispatch_wgrad<DT_BF16>(opt, st, tm_dy, tm_x, tm_w, tm_m, tm_v, p, grid, stream);
-  return dispatch_wgrad<DT_F32>(opt, st, tm_dy, tm_x, tm_w, tm_m, tm_v, p, grid, stream);
+  if (a.w_dtype == FORGE_DT_BF16) return dispatch_wgrad<DT_BF16>(opt, st, tm_dy, tm_x, t, p, grid, stream);
+  return dispatch_wgrad<DT_F32>(opt, st, tm_dy, tm_x, t, p, grid, stream);
 }

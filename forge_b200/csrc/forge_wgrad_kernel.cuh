@@ -13,10 +13,14 @@
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), frees it
 //   warp 2      TMA producer of the W / moment sub-tiles (prefetched while the MMAs of the tile run)
 //   warp 3      idle
-//   warps 4-11  epilogue: two groups of four warps; group g handles the 64-column chunks g and g+2
-//               of the 128 x 256 tile.  Each thread owns one accumulator row: tcgen05.ld, fp32
-//               update against the staged W/moment rows in shared memory (in place), then one TMA
-//               store per warp and tensor.
+//   warps 4-11  epilogue: two groups of four warps; group g handles the column chunks g, g+2, ...
+//               of the 128 x 256 tile (chunks are 64 columns wide, 32 when W or the moments are
+//               fp32 and a 64-column stage would not fit twice).  Each thread owns one accumulator
+//               row: tcgen05.ld, fp32 update against the staged W/moment rows in shared memory (in
+//               place), then one TMA store per warp and tensor.
+// The ring of state stages has an even number of slots, so the chunks of group g always land in
+// slots of parity g: every full/empty barrier then has a single consumer group that observes each
+// of its phases, which is what makes waiting on the phase parity sound.
 // Tensor memory holds two 128 x 256 fp32 accumulators, so the MMAs of tile i+1 overlap the
 // epilogue of tile i.
 #pragma once
@@ -28,9 +32,18 @@ namespace forge {
 
 constexpr int TILE_M = 128;        // rows of W per tile (V direction)
 constexpr int TILE_N = 256;        // columns of W per tile (H direction)
-constexpr int CHUNK_N = 64;        // columns per epilogue chunk
-constexpr int NUM_CHUNKS = TILE_N / CHUNK_N;
 constexpr int UMMA_K = 16;
+#ifndef FORGE_OP_BK
+#define FORGE_OP_BK 32
+#endif
+#ifndef FORGE_OP_STAGES
+#define FORGE_OP_STAGES 3
+#endif
+#ifndef FORGE_MAX_STATE_STAGES
+#define FORGE_MAX_STATE_STAGES 6
+#endif
+constexpr int OP_BK = FORGE_OP_BK;           // token rows per operand pipeline stage
+constexpr int OP_STAGES = FORGE_OP_STAGES;   // operand pipeline depth
 constexpr int NUM_THREADS = 384;
 constexpr int EPI_WARP0 = 4;
 constexpr int NUM_EPI_WARPS = 8;
@@ -47,25 +60,25 @@ enum : int {
   ERR_WAIT_ACC_FULL = 106
 };
 
-template <int ES>
-struct BoxGeom;  // geometry of one 128-row x 64-column chunk of a tensor with ES-byte elements
+// Geometry of one 128-row chunk of a tensor whose rows are RB bytes wide inside the chunk.
+template <int RB>
+struct BoxGeom;
 template <>
-struct BoxGeom<2> {  // one box: 64 columns = 128 bytes per row, 128-byte swizzle
-  static constexpr int kBoxes = 1, kBoxCols = 64, kPitch = 128, kBoxBytes = 128 * 128;
+struct BoxGeom<256> {  // two boxes of 128 bytes per row each, 128-byte swizzle (fp32, 64 columns)
+  static constexpr int kBoxes = 2, kBoxRowBytes = 128, kPitch = 128, kBoxBytes = 128 * 128, kSwizzle = 128;
 };
 template <>
-struct BoxGeom<4> {  // two boxes of 32 columns = 128 bytes per row each, 128-byte swizzle
-  static constexpr int kBoxes = 2, kBoxCols = 32, kPitch = 128, kBoxBytes = 128 * 128;
+struct BoxGeom<128> {  // one box, 128 bytes per row, 128-byte swizzle
+  static constexpr int kBoxes = 1, kBoxRowBytes = 128, kPitch = 128, kBoxBytes = 128 * 128, kSwizzle = 128;
 };
 template <>
-struct BoxGeom<1> {  // one box: 64 columns = 64 bytes per row, 64-byte swizzle
-  static constexpr int kBoxes = 1, kBoxCols = 64, kPitch = 64, kBoxBytes = 128 * 64;
+struct BoxGeom<64> {  // one box, 64 bytes per row, 64-byte swizzle
+  static constexpr int kBoxes = 1, kBoxRowBytes = 64, kPitch = 64, kBoxBytes = 128 * 64, kSwizzle = 64;
 };
-
-template <int ES>
-__host__ __device__ constexpr int chunk_bytes() {
-  return 128 * CHUNK_N * ES;
-}
+template <>
+struct BoxGeom<0> {  // absent tensor
+  static constexpr int kBoxes = 0, kBoxRowBytes = 16, kPitch = 0, kBoxBytes = 0, kSwizzle = 0;
+};
 
 __host__ __device__ constexpr int num_moments(int opt) {
   return opt == OPT_ADAMW ? 2 : (opt == OPT_SGD ? 0 : 1);
@@ -74,33 +87,55 @@ __host__ __device__ constexpr int state_elem_size(int st) {
   return st == ST_F32 ? 4 : (st == ST_BF16 ? 2 : (st == ST_NONE ? 0 : 1));
 }
 
-// byte offset of the 16-byte piece `j` of row `r` inside a chunk buffer
-template <int ES>
+// byte offset of the 16-byte piece `j` of row `r` inside a chunk buffer with RB-byte rows
+template <int RB>
 __device__ __forceinline__ uint32_t piece_off(int r, int j) {
-  if constexpr (ES == 2) {
+  if constexpr (RB == 256) {
+    return (j >> 3) * BoxGeom<256>::kBoxBytes + r * 128 + (((j & 7) ^ (r & 7)) << 4);
+  } else if constexpr (RB == 128) {
     return r * 128 + ((j ^ (r & 7)) << 4);
-  } else if constexpr (ES == 4) {
-    return (j >> 3) * BoxGeom<4>::kBoxBytes + r * 128 + (((j & 7) ^ (r & 7)) << 4);
   } else {
+    static_assert(RB == 64, "row bytes");
     return r * 64 + ((j ^ ((r >> 1) & 3)) << 4);
   }
 }
 
-// ---- 16-element row-group loads / stores between shared memory and fp32 registers -------------
+// ---- 16-element row groups: raw 16-byte pieces <-> fp32 registers --------------------------------
+// The raw pieces of the NEXT group are fetched before the current group is computed and stored
+// (shared-memory loads cannot be hoisted over stores by the compiler, the swizzled addresses defeat
+// its alias analysis), so load latency overlaps arithmetic.
 template <int ES>
-__device__ __forceinline__ void ld16_float(const uint8_t* buf, int r, int g, float (&out)[16]) {
+struct Raw16 {
+  uint4 q[ES];   // 16 elements: one piece of codes, two of bf16, four of fp32
+};
+
+template <int ES, int RB>
+__device__ __forceinline__ Raw16<ES> load_raw(const uint8_t* buf, int r, int g) {
+  Raw16<ES> x;
+#pragma unroll
+  for (int p = 0; p < ES; ++p) x.q[p] = *reinterpret_cast<const uint4*>(buf + piece_off<RB>(r, ES * g + p));
+  return x;
+}
+
+template <int ES, int RB>
+__device__ __forceinline__ void store_raw(uint8_t* buf, int r, int g, const Raw16<ES>& x) {
+#pragma unroll
+  for (int p = 0; p < ES; ++p) *reinterpret_cast<uint4*>(buf + piece_off<RB>(r, ES * g + p)) = x.q[p];
+}
+
+template <int ES>
+__device__ __forceinline__ void unpack16(const Raw16<ES>& x, float (&out)[16]) {
   if constexpr (ES == 4) {
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
-      const float4 q = *reinterpret_cast<const float4*>(buf + piece_off<4>(r, 4 * g + p));
-      out[4 * p + 0] = q.x; out[4 * p + 1] = q.y; out[4 * p + 2] = q.z; out[4 * p + 3] = q.w;
+      out[4 * p + 0] = __uint_as_float(x.q[p].x); out[4 * p + 1] = __uint_as_float(x.q[p].y);
+      out[4 * p + 2] = __uint_as_float(x.q[p].z); out[4 * p + 3] = __uint_as_float(x.q[p].w);
     }
   } else {
     static_assert(ES == 2, "float/bf16 only");
 #pragma unroll
     for (int p = 0; p < 2; ++p) {
-      const uint4 q = *reinterpret_cast<const uint4*>(buf + piece_off<2>(r, 2 * g + p));
-      const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+      const uint32_t u[4] = {x.q[p].x, x.q[p].y, x.q[p].z, x.q[p].w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         out[8 * p + 2 * i + 0] = __uint_as_float(u[i] << 16);
@@ -110,35 +145,37 @@ __device__ __forceinline__ void ld16_float(const uint8_t* buf, int r, int g, flo
   }
 }
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
 template <int ES>
-__device__ __forceinline__ void st16_float(uint8_t* buf, int r, int g, const float (&in)[16]) {
+__device__ __forceinline__ Raw16<ES> pack16(const float (&in)[16]) {
+  Raw16<ES> x;
   if constexpr (ES == 4) {
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      *reinterpret_cast<float4*>(buf + piece_off<4>(r, 4 * g + p)) =
-          make_float4(in[4 * p + 0], in[4 * p + 1], in[4 * p + 2], in[4 * p + 3]);
-    }
+    for (int p = 0; p < 4; ++p)
+      x.q[p] = make_uint4(__float_as_uint(in[4 * p + 0]), __float_as_uint(in[4 * p + 1]),
+                          __float_as_uint(in[4 * p + 2]), __float_as_uint(in[4 * p + 3]));
   } else {
     static_assert(ES == 2, "float/bf16 only");
 #pragma unroll
-    for (int p = 0; p < 2; ++p) {
-      uint32_t u[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        u[i] = float_to_bf16_bits(in[8 * p + 2 * i + 0]) |
-               (float_to_bf16_bits(in[8 * p + 2 * i + 1]) << 16);
-      }
-      *reinterpret_cast<uint4*>(buf + piece_off<2>(r, 2 * g + p)) = make_uint4(u[0], u[1], u[2], u[3]);
-    }
+    for (int p = 0; p < 2; ++p)
+      x.q[p] = make_uint4(pack_bf16x2(in[8 * p + 0], in[8 * p + 1]), pack_bf16x2(in[8 * p + 2], in[8 * p + 3]),
+                          pack_bf16x2(in[8 * p + 4], in[8 * p + 5]), pack_bf16x2(in[8 * p + 6], in[8 * p + 7]));
   }
+  return x;
 }
 
+// one-byte codes: 64-column chunks only (row = 64 bytes)
 __device__ __forceinline__ void ld16_bytes(const uint8_t* buf, int r, int g, uint32_t (&w)[4]) {
-  const uint4 q = *reinterpret_cast<const uint4*>(buf + piece_off<1>(r, g));
+  const uint4 q = *reinterpret_cast<const uint4*>(buf + piece_off<64>(r, g));
   w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
 }
 __device__ __forceinline__ void st16_bytes(uint8_t* buf, int r, int g, const uint32_t (&w)[4]) {
-  *reinterpret_cast<uint4*>(buf + piece_off<1>(r, g)) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4*>(buf + piece_off<64>(r, g)) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 // kernel parameters ------------------------------------------------------------------------------
@@ -155,9 +192,9 @@ struct WgradParams {
   int* status;         // device status word: 0 = ok
 };
 
-template <int BK, int NSTAGE>
-__host__ __device__ constexpr int op_stage_bytes() {
-  return (TILE_M + TILE_N) * BK * 2;
+// bytes one pipeline stage of W + moments takes for a chunk of `cn` columns
+__host__ __device__ constexpr int state_stage_bytes(int wes, int ses, int nmom, int cn) {
+  return 128 * cn * (wes + nmom * ses);
 }
 
 template <int W_DT, int ST, int OPT>
@@ -165,26 +202,33 @@ struct WgradCfg {
   static constexpr int kWES = (W_DT == DT_BF16) ? 2 : 4;
   static constexpr int kNMom = num_moments(OPT);
   static constexpr int kSES = state_elem_size(ST);
-  static constexpr int kWBytes = chunk_bytes<kWES>();
-  static constexpr int kSBytes = (kNMom > 0) ? 128 * CHUNK_N * kSES : 0;
-  static constexpr int kStageBytes = kWBytes + kNMom * kSBytes;
-  static constexpr int kBK = 64;
+  static constexpr int kBK = OP_BK;
+  static constexpr int kNStage = OP_STAGES;
   static constexpr int kOpStageBytes = (TILE_M + TILE_N) * kBK * 2;
   static constexpr int kCtrlBytes = 1024;
-  // two operand stages when that still leaves room for two state stages, else fit what we can
-  static constexpr int kNStage = 2;
   static constexpr int kRoom = SMEM_BUDGET - kCtrlBytes - 1024 - kNStage * kOpStageBytes;
+  // 64-column chunks when four such stages fit (always with one-byte codes, whose quantisation block
+  // is 64 columns); otherwise 32-column chunks, which buy a deeper ring for the same bytes
+  static constexpr int kCN = (kSES == 1 || 4 * state_stage_bytes(kWES, kSES, kNMom, 64) <= kRoom) ? 64 : 32;
+  static constexpr int kNumChunks = TILE_N / kCN;
+  static constexpr int kWRB = kCN * kWES;                      // bytes per W row inside a chunk
+  static constexpr int kSRB = (kNMom > 0) ? kCN * kSES : 0;    // bytes per moment row inside a chunk
+  static constexpr int kWBytes = 128 * kWRB;
+  static constexpr int kSBytes = 128 * kSRB;
+  static constexpr int kStageBytes = kWBytes + kNMom * kSBytes;
   static constexpr int kNSS_raw = kRoom / kStageBytes;
-  static constexpr int kNSS = kNSS_raw > 4 ? 4 : kNSS_raw;
+  static constexpr int kNSS_cap = kNSS_raw >= 6 ? 6 : (kNSS_raw >= 4 ? 4 : 2);   // even, see the file comment
+  static constexpr int kNSS = kNSS_cap > FORGE_MAX_STATE_STAGES ? FORGE_MAX_STATE_STAGES : kNSS_cap;
   static constexpr int kSmemBytes = kCtrlBytes + 1024 + kNStage * kOpStageBytes + kNSS * kStageBytes;
-  static_assert(kNSS >= 1, "state stage does not fit in shared memory");
+  static_assert(kNSS_raw >= 2, "two state stages must fit in shared memory");
+  static_assert(kSES != 1 || kCN == 64, "one-byte codes need 64-column chunks (the quantisation block)");
 };
 
 struct alignas(8) CtrlBlock {
-  uint64_t op_full[4];
-  uint64_t op_empty[4];
-  uint64_t st_full[4];
-  uint64_t st_empty[4];
+  uint64_t op_full[8];
+  uint64_t op_empty[8];
+  uint64_t st_full[6];
+  uint64_t st_empty[6];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -204,6 +248,13 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
   constexpr int WES = Cfg::kWES;
   constexpr int SES = Cfg::kSES;
   constexpr int NMOM = Cfg::kNMom;
+  constexpr int CN = Cfg::kCN;                 // columns per chunk
+  constexpr int NCH = Cfg::kNumChunks;         // chunks per tile
+  constexpr int NG = CN / 16;                  // 16-column groups per chunk
+  constexpr int WRB = Cfg::kWRB;
+  constexpr int SRB = Cfg::kSRB;
+  constexpr int WBC = BoxGeom<WRB>::kBoxRowBytes / WES;                 // columns per W box
+  constexpr int SBC = (NMOM > 0) ? BoxGeom<SRB>::kBoxRowBytes / (SES > 0 ? SES : 1) : 1;
   constexpr int A_BYTES = TILE_M * BK * 2;
   constexpr int B_BYTES = TILE_N * BK * 2;
   constexpr int SLAB_BYTES = 64 * BK * 2;  // one 64-element M/N slab of a K panel
@@ -302,38 +353,42 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
   } else if (warp == 2) {
     // ------------------------------------------------------------------ state producer
     if (lane == 0) {
-      const uint64_t pol = policy_evict_first();
+      // Normal priority, not evict-first: a chunk row is only 64-128 bytes, the L2 fetches 256-byte
+      // granules, and the rest of each granule is wanted by the next chunks a few microseconds
+      // later.  With evict-first those lines were dropped and fetched again (measured: 158 us ->
+      // 126 us on a 14336 x 4096 bf16 update when this policy was changed).
+      const uint64_t pol = policy_evict_normal();
       uint32_t q = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
         const int row0 = (tile / p.tiles_n) * TILE_M;
         const int col0 = (tile % p.tiles_n) * TILE_N;
-        for (int c = 0; c < NUM_CHUNKS; ++c, ++q) {
+        for (int c = 0; c < NCH; ++c, ++q) {
           const int s = q % NSS;
           const uint32_t ph = (q / NSS) & 1;
           if (!mbar_wait(&ctrl->st_empty[s], ph ^ 1, abort_word, ERR_WAIT_ST_EMPTY)) goto done;
           uint8_t* wb = st_buf + s * Cfg::kStageBytes;
           mbar_expect_tx(&ctrl->st_full[s], Cfg::kStageBytes);
-          const int cc = col0 + c * CHUNK_N;
+          const int cc = col0 + c * CN;
 #pragma unroll
           for (int rb = 0; rb < 4; ++rb) {
             const int rr = row0 + 32 * rb;
 #pragma unroll
-            for (int bx = 0; bx < BoxGeom<WES>::kBoxes; ++bx)
-              tma_load_2d(wb + bx * BoxGeom<WES>::kBoxBytes + rb * 32 * BoxGeom<WES>::kPitch, &tm_w,
-                          &ctrl->st_full[s], cc + bx * BoxGeom<WES>::kBoxCols, rr, pol);
+            for (int bx = 0; bx < BoxGeom<WRB>::kBoxes; ++bx)
+              tma_load_2d(wb + bx * BoxGeom<WRB>::kBoxBytes + rb * 32 * BoxGeom<WRB>::kPitch, &tm_w,
+                          &ctrl->st_full[s], cc + bx * WBC, rr, pol);
             if constexpr (NMOM > 0) {
               uint8_t* mb = wb + Cfg::kWBytes;
 #pragma unroll
-              for (int bx = 0; bx < BoxGeom<SES>::kBoxes; ++bx)
-                tma_load_2d(mb + bx * BoxGeom<SES>::kBoxBytes + rb * 32 * BoxGeom<SES>::kPitch, &tm_m,
-                            &ctrl->st_full[s], cc + bx * BoxGeom<SES>::kBoxCols, rr, pol);
+              for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
+                tma_load_2d(mb + bx * BoxGeom<SRB>::kBoxBytes + rb * 32 * BoxGeom<SRB>::kPitch, &tm_m,
+                            &ctrl->st_full[s], cc + bx * SBC, rr, pol);
             }
             if constexpr (NMOM > 1) {
               uint8_t* vb = wb + Cfg::kWBytes + Cfg::kSBytes;
 #pragma unroll
-              for (int bx = 0; bx < BoxGeom<SES>::kBoxes; ++bx)
-                tma_load_2d(vb + bx * BoxGeom<SES>::kBoxBytes + rb * 32 * BoxGeom<SES>::kPitch, &tm_v,
-                            &ctrl->st_full[s], cc + bx * BoxGeom<SES>::kBoxCols, rr, pol);
+              for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
+                tma_load_2d(vb + bx * BoxGeom<SRB>::kBoxBytes + rb * 32 * BoxGeom<SRB>::kPitch, &tm_v,
+                            &ctrl->st_full[s], cc + bx * SBC, rr, pol);
             }
           }
         }
@@ -345,7 +400,8 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
     const int wg = (warp - EPI_WARP0) >> 2;       // 0 or 1
     const int r = quarter * 32 + lane;            // row inside the tile
     const Hyper hy = p.hyper;
-    const uint64_t pol = policy_evict_first();
+    // stores: normal priority, so that the partial lines of neighbouring chunks merge in L2
+    const uint64_t pol = policy_evict_normal();
     float s_m_t = 1.0f, s_v_t = 1.0f, inv_m_t = 1.0f, inv_v_t = 1.0f;
     float amax_m_t = 0.0f, amax_v_t = 0.0f;
     if constexpr (ST == ST_FP8_TENSOR) {
@@ -356,6 +412,19 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
     }
     uint32_t tile_it = 0;
     bool ok = true;
+    int held_stage = -1;   // stage whose TMA store may still be reading shared memory
+    // Give the previous chunk's stage back to the producer.  Called a little way into the next
+    // chunk's arithmetic, by which time the TMA engine has long finished reading the stage, so the
+    // wait does not block and the stage spends almost all of its life loading or being computed on.
+    auto release_held = [&]() {
+      if (held_stage >= 0) {
+        if (lane == 0) {
+          tma_store_wait_read<0>();
+          mbar_arrive(&ctrl->st_empty[held_stage]);
+        }
+        held_stage = -1;
+      }
+    };
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
       const int row0 = (tile / p.tiles_n) * TILE_M;
       const int col0 = (tile % p.tiles_n) * TILE_N;
@@ -382,19 +451,19 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
       tc_fence_after();
 
 #pragma unroll 1
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < NCH / 2; ++i) {
         const int c = wg + 2 * i;
-        const uint32_t q = tile_it * NUM_CHUNKS + c;
+        const uint32_t q = tile_it * NCH + c;
         const int s = q % NSS;
         const uint32_t ph = (q / NSS) & 1;
 
-        // accumulator row: 64 fp32 columns of this chunk
-        uint32_t acc[64];
+        // accumulator row: the CN fp32 columns of this chunk
+        uint32_t acc[CN];
         {
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                 static_cast<uint32_t>(buf * TILE_N + c * CHUNK_N);
+                                 static_cast<uint32_t>(buf * TILE_N + c * CN);
           tmem_ld_32x32(taddr, &acc[0]);
-          tmem_ld_32x32(taddr + 32, &acc[32]);
+          if constexpr (CN == 64) tmem_ld_32x32(taddr + 32, &acc[32]);
         }
         ok = mbar_wait(&ctrl->st_full[s], ph, abort_word, ERR_WAIT_ST_FULL);
         ok = __all_sync(0xffffffffu, ok);
@@ -402,7 +471,7 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
         if (!ok) break;
         if (p.num_kb == 0) {
 #pragma unroll
-          for (int k = 0; k < 64; ++k) acc[k] = 0u;
+          for (int k = 0; k < CN; ++k) acc[k] = 0u;
         }
 
         uint8_t* wb = st_buf + s * Cfg::kStageBytes;
@@ -410,51 +479,79 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
         uint8_t* vb = mb + Cfg::kSBytes;
 
         if constexpr (OPT == OPT_SGD) {
+          Raw16<WES> rw = load_raw<WES, WRB>(wb, r, 0);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int g = 0; g < NG; ++g) {
+            Raw16<WES> nw;
+            if (g + 1 < NG) nw = load_raw<WES, WRB>(wb, r, g + 1);
             float w[16];
-            ld16_float<WES>(wb, r, g, w);
+            unpack16<WES>(rw, w);
 #pragma unroll
             for (int k = 0; k < 16; ++k) w[k] = sgd_update(w[k], __uint_as_float(acc[16 * g + k]), hy);
-            st16_float<WES>(wb, r, g, w);
+            store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
+            if (g + 1 < NG) rw = nw;
+            if (g == 0) release_held();
           }
         } else if constexpr (OPT == OPT_SGDM || OPT == OPT_LION) {
+          Raw16<WES> rw = load_raw<WES, WRB>(wb, r, 0);
+          Raw16<SES> rm = load_raw<SES, SRB>(mb, r, 0);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int g = 0; g < NG; ++g) {
+            Raw16<WES> nw;
+            Raw16<SES> nm;
+            if (g + 1 < NG) {
+              nw = load_raw<WES, WRB>(wb, r, g + 1);
+              nm = load_raw<SES, SRB>(mb, r, g + 1);
+            }
             float w[16], m[16];
-            ld16_float<WES>(wb, r, g, w);
-            ld16_float<SES>(mb, r, g, m);
+            unpack16<WES>(rw, w);
+            unpack16<SES>(rm, m);
 #pragma unroll
             for (int k = 0; k < 16; ++k) {
               const float gr = __uint_as_float(acc[16 * g + k]);
               w[k] = (OPT == OPT_SGDM) ? sgdm_update(w[k], gr, m[k], hy) : lion_update(w[k], gr, m[k], hy);
             }
-            st16_float<WES>(wb, r, g, w);
-            st16_float<SES>(mb, r, g, m);
+            store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
+            store_raw<SES, SRB>(mb, r, g, pack16<SES>(m));
+            if (g + 1 < NG) { rw = nw; rm = nm; }
+            if (g == 0) release_held();
           }
         } else if constexpr (ST == ST_F32 || ST == ST_BF16) {
+          Raw16<WES> rw = load_raw<WES, WRB>(wb, r, 0);
+          Raw16<SES> rm = load_raw<SES, SRB>(mb, r, 0);
+          Raw16<SES> rv = load_raw<SES, SRB>(vb, r, 0);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int g = 0; g < NG; ++g) {
+            Raw16<WES> nw;
+            Raw16<SES> nm, nv;
+            if (g + 1 < NG) {
+              nw = load_raw<WES, WRB>(wb, r, g + 1);
+              nm = load_raw<SES, SRB>(mb, r, g + 1);
+              nv = load_raw<SES, SRB>(vb, r, g + 1);
+            }
             float w[16], m[16], v[16];
-            ld16_float<WES>(wb, r, g, w);
-            ld16_float<SES>(mb, r, g, m);
-            ld16_float<SES>(vb, r, g, v);
+            unpack16<WES>(rw, w);
+            unpack16<SES>(rm, m);
+            unpack16<SES>(rv, v);
 #pragma unroll
             for (int k = 0; k < 16; ++k)
               w[k] = adamw_update(w[k], __uint_as_float(acc[16 * g + k]), m[k], v[k], hy);
-            st16_float<WES>(wb, r, g, w);
-            st16_float<SES>(mb, r, g, m);
-            st16_float<SES>(vb, r, g, v);
+            store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
+            store_raw<SES, SRB>(mb, r, g, pack16<SES>(m));
+            store_raw<SES, SRB>(vb, r, g, pack16<SES>(v));
+            if (g + 1 < NG) { rw = nw; rm = nm; rv = nv; }
+            if (g == 0) release_held();
           }
         } else if constexpr (ST == ST_INT8 || ST == ST_FP8_BLOCK) {
           // pass 1: dequantise, update W, find the block absmax of the new moments
-          const float sm_old = sc_m[i], sv_old = sc_v[i];
+          const float sm_old = (i == 0) ? sc_m[0] : sc_m[1];
+          const float sv_old = (i == 0) ? sc_v[0] : sc_v[1];
           float am = 0.0f, av = 0.0f;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int g = 0; g < NG; ++g) {
             float w[16];
             uint32_t mq[4], vq[4];
-            ld16_float<WES>(wb, r, g, w);
+            unpack16<WES>(load_raw<WES, WRB>(wb, r, g), w);
             ld16_bytes(mb, r, g, mq);
             ld16_bytes(vb, r, g, vq);
 #pragma unroll
@@ -473,13 +570,15 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
               am = fmaxf(am, fabsf(m));
               av = fmaxf(av, fabsf(v));
             }
-            st16_float<WES>(wb, r, g, w);
+            store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
+            if (g == 0) release_held();
           }
           const float sm_new = (ST == ST_INT8) ? int8_scale(am) : fp8blk_scale(am);
           const float sv_new = (ST == ST_INT8) ? int8_scale(av) : fp8blk_scale(av);
+          const float rsm = f_div(1.0f, sm_new), rsv = f_div(1.0f, sv_new);
           // pass 2: recompute the new moments (same instruction sequence) and requantise
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int g = 0; g < NG; ++g) {
             uint32_t mq[4], vq[4], mo[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
             ld16_bytes(mb, r, g, mq);
             ld16_bytes(vb, r, g, vq);
@@ -500,11 +599,11 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
               v = f_add(f_mul(hy.beta2, v), f_mul(f_mul(hy.one_m_beta2, gr), gr));
               uint32_t mc, vc;
               if constexpr (ST == ST_INT8) {
-                mc = static_cast<uint32_t>(int8_code(m, sm_new)) & 0xFFu;
-                vc = static_cast<uint32_t>(int8_code(v, sv_new)) & 0xFFu;
+                mc = static_cast<uint32_t>(int8_code(m, sm_new, rsm)) & 0xFFu;
+                vc = static_cast<uint32_t>(int8_code(v, sv_new, rsv)) & 0xFFu;
               } else {
-                mc = e4m3_code(f_div(m, sm_new));
-                vc = e4m3_code(f_div(v, sv_new));
+                mc = e4m3_code(div_by_rcp(m, sm_new, rsm));
+                vc = e4m3_code(div_by_rcp(v, sv_new, rsv));
               }
               mo[k >> 2] |= mc << (8 * (k & 3));
               vo[k >> 2] |= vc << (8 * (k & 3));
@@ -521,10 +620,10 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           }
         } else {  // ST_FP8_TENSOR
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int g = 0; g < NG; ++g) {
             float w[16];
             uint32_t mq[4], vq[4], mo[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
-            ld16_float<WES>(wb, r, g, w);
+            unpack16<WES>(load_raw<WES, WRB>(wb, r, g), w);
             ld16_bytes(mb, r, g, mq);
             ld16_bytes(vb, r, g, vq);
 #pragma unroll
@@ -541,9 +640,10 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
               mo[k >> 2] |= static_cast<uint32_t>(e4m3_code(f_mul(m, inv_m_t))) << (8 * (k & 3));
               vo[k >> 2] |= static_cast<uint32_t>(e5m2_code(f_mul(v, inv_v_t))) << (8 * (k & 3));
             }
-            st16_float<WES>(wb, r, g, w);
+            store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
             st16_bytes(mb, r, g, mo);
             st16_bytes(vb, r, g, vo);
+            if (g == 0) release_held();
           }
         }
 
@@ -552,32 +652,37 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
         __syncwarp();
         if (lane == 0) {
           const int rr = row0 + quarter * 32;
-          const int cc = col0 + c * CHUNK_N;
+          const int cc = col0 + c * CN;
           if (rr < p.V && cc < p.H) {
 #pragma unroll
-            for (int bx = 0; bx < BoxGeom<WES>::kBoxes; ++bx)
-              if (cc + bx * BoxGeom<WES>::kBoxCols < p.H)
-                tma_store_2d(&tm_w, wb + bx * BoxGeom<WES>::kBoxBytes + quarter * 32 * BoxGeom<WES>::kPitch,
-                             cc + bx * BoxGeom<WES>::kBoxCols, rr, pol);
+            for (int bx = 0; bx < BoxGeom<WRB>::kBoxes; ++bx)
+              if (cc + bx * WBC < p.H)
+                tma_store_2d(&tm_w, wb + bx * BoxGeom<WRB>::kBoxBytes + quarter * 32 * BoxGeom<WRB>::kPitch,
+                             cc + bx * WBC, rr, pol);
             if constexpr (NMOM > 0) {
 #pragma unroll
-              for (int bx = 0; bx < BoxGeom<SES>::kBoxes; ++bx)
-                if (cc + bx * BoxGeom<SES>::kBoxCols < p.H)
-                  tma_store_2d(&tm_m, mb + bx * BoxGeom<SES>::kBoxBytes + quarter * 32 * BoxGeom<SES>::kPitch,
-                               cc + bx * BoxGeom<SES>::kBoxCols, rr, pol);
+              for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
+                if (cc + bx * SBC < p.H)
+                  tma_store_2d(&tm_m, mb + bx * BoxGeom<SRB>::kBoxBytes + quarter * 32 * BoxGeom<SRB>::kPitch,
+                               cc + bx * SBC, rr, pol);
             }
             if constexpr (NMOM > 1) {
 #pragma unroll
-              for (int bx = 0; bx < BoxGeom<SES>::kBoxes; ++bx)
-                if (cc + bx * BoxGeom<SES>::kBoxCols < p.H)
-                  tma_store_2d(&tm_v, vb + bx * BoxGeom<SES>::kBoxBytes + quarter * 32 * BoxGeom<SES>::kPitch,
-                               cc + bx * BoxGeom<SES>::kBoxCols, rr, pol);
+              for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
+                if (cc + bx * SBC < p.H)
+                  tma_store_2d(&tm_v, vb + bx * BoxGeom<SRB>::kBoxBytes + quarter * 32 * BoxGeom<SRB>::kPitch,
+                               cc + bx * SBC, rr, pol);
             }
           }
           tma_store_commit();
-          tma_store_wait_read<0>();          // the stage may be refilled once the engine has read it
-          mbar_arrive(&ctrl->st_empty[s]);
+          if constexpr (NSS < 4) {
+            // a group with a single stage cannot hold it across chunks
+            tma_store_wait_read<0>();
+            mbar_arrive(&ctrl->st_empty[s]);
+          }
         }
+        release_held();                       // no-op unless the chunk had a single group
+        held_stage = (NSS >= 4) ? s : -1;
         __syncwarp();
       }
       if (!ok) break;
@@ -586,6 +691,7 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctrl->acc_empty[buf]);
     }
+    release_held();
     if (lane == 0) tma_store_wait_all<0>();
     if constexpr (ST == ST_FP8_TENSOR) {
 #pragma unroll

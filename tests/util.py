@@ -75,3 +75,40 @@ def assert_bits_equal(expected: np.ndarray, actual: torch.Tensor, what: str):
         e = torch.from_numpy(expected.view(np.uint8))
         av = a.view(torch.uint8)
         assert torch.equal(e, av), f"{what}: codes differ ({(e != av).sum().item()} elements)"
+
+
+def bf16_ulp(x: torch.Tensor) -> torch.Tensor:
+    """Size of one bf16 ULP at magnitude |x| (8 significand bits), with a floor at the smallest normal."""
+    ax = x.abs().double().clamp_min(2.0 ** -126)
+    return torch.pow(2.0, torch.floor(torch.log2(ax)) - 7)
+
+
+def assert_one_ulp(expected, actual: torch.Tensor, scale, what: str, noise=4e-6):
+    """|actual - expected| <= one bf16 ULP of the expected value + fp32 summation noise at the scale
+    of the terms that were added (`scale`, tensor or float).  The ULP term covers a rounding that
+    flips at a bf16 boundary; the noise term covers results that cancelled to far below their
+    operands, where a distance counted in ULPs of the result is meaningless."""
+    if isinstance(expected, np.ndarray):
+        expected = torch.from_numpy(expected)
+    e = expected.double()
+    a = actual.detach().cpu().double()
+    sc = scale.double().abs() if isinstance(scale, torch.Tensor) else torch.full_like(e, float(scale))
+    # one ULP of whichever of the two values lies in the larger binade, plus the noise floor
+    tol = torch.maximum(bf16_ulp(e), bf16_ulp(a)) + noise * sc
+    bad = (a - e).abs() > tol
+    assert not bad.any(), (f"{what}: {int(bad.sum())} elements beyond one bf16 ULP; worst "
+                           f"{((a - e).abs() / tol).max().item():.2f}x the bound")
+
+
+def assert_w_close(expected, actual: torch.Tensor, w_in: torch.Tensor, what="W"):
+    """AdamW weight: within one bf16 ULP of the oracle (the device evaluates the bias-corrected
+    quotient with approximate reciprocal / square root); fp32 weights additionally within fp32
+    noise of the update."""
+    if isinstance(expected, np.ndarray):
+        expected = torch.from_numpy(expected)
+    scale = w_in.detach().cpu().float().abs() + 1e-2
+    assert_one_ulp(expected, actual, scale, what, noise=1e-6)
+    if actual.dtype == torch.float32:
+        d = (actual.detach().cpu().double() - expected.double()).abs()
+        bound = 1e-7 + 1e-6 * w_in.detach().cpu().double().abs()
+        assert (d <= bound).all(), f"{what}: fp32 weight off by {d.max().item():.3e}"
