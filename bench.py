@@ -1,0 +1,411 @@
+"""Benchmark of the fused weight-gradient + AdamW path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl forge|reference] [--workload NAME]
+
+Workload (default ``llama3.1-8b-linears``): every linear of the Llama-3.1-8B architecture that the
+reference fuses -- 32 decoder layers x (q 4096x4096, k 1024x4096, v 1024x4096, o 4096x4096,
+gate 14336x4096, up 14336x4096, down 4096x14336) plus lm_head 128256x4096 -- at BT = 512 tokens,
+bf16 weights and bf16 AdamW moments, random-initialised, synthetic activations X ~ N(0,1) and
+gradients dY ~ N(0, 1e-2) in bf16.  A *step* is one fused wgrad+AdamW update of each of the 225
+weights (one kernel launch each).  Every weight and its moments are distinct buffers (45 GB in
+total), so each launch streams cold state; only the small X / dY panels may sit in L2, as they do in
+training where the preceding kernel has just produced them.
+
+``value``  ms per step with X / dY already resident in device memory (CUDA events around the K
+           timed steps on the launching stream, max over ranks).
+``e2e``    the same step through the public operator API with HOST inputs: every launch first copies
+           its X and dY from pinned host memory, and each step ends with a device-to-host read of a
+           status word and one updated weight.
+N > 1      row-sharded tensor parallelism: rank r owns rows [r V/N, (r+1) V/N) of every weight and
+           moment; X arrives feature-sharded and is all-gathered by NCCL once per group of linears
+           that share it (q/k/v, gate/up, o, down, lm_head) inside the timed step; strong scaling.
+``--impl reference``  the reference's own CPU-runnable path for this update -- torch autograd +
+           ``torch.optim.AdamW`` on the host cores -- on a bounded sample (one decoder layer's seven
+           projections), scaled to the full workload by parameter count.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BT = 512
+HIDDEN, KV, FFN, VOCAB, LAYERS = 4096, 1024, 14336, 128256, 32
+# name, V (out), H (in), group that shares one gathered X
+LAYER_LINEARS = [("q", HIDDEN, HIDDEN, "attn_in"), ("k", KV, HIDDEN, "attn_in"), ("v", KV, HIDDEN, "attn_in"),
+                 ("o", HIDDEN, HIDDEN, "attn_out"), ("gate", FFN, HIDDEN, "mlp_in"), ("up", FFN, HIDDEN, "mlp_in"),
+                 ("down", HIDDEN, FFN, "mlp_out")]
+HYPER = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01)
+
+
+def workload_linears(name):
+    if name == "llama3.1-8b-linears":
+        lin = [(f"l{i}.{n}", V, H, f"l{i}.{g}") for i in range(LAYERS) for n, V, H, g in LAYER_LINEARS]
+        lin.append(("lm_head", VOCAB, HIDDEN, "lm_head"))
+        return lin
+    if name == "llama3.1-8b-layer":   # one decoder layer: the projection set of BASELINE configuration 1
+        return [(n, V, H, g) for n, V, H, g in LAYER_LINEARS]
+    raise SystemExit(f"unknown workload {name}")
+
+
+def algorithmic_bytes(V, H, bt=BT, state_bytes=6):
+    """read W,m,v + write W,m,v + read X once + read dY once (bf16 W, bf16 moments)."""
+    return 2 * state_bytes * V * H + 2 * bt * (V + H)
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except OSError:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "50"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [t.strip() for t in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            busy = [s for s in sm if s >= 0.5 * max(sm)] or sm
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference(args):
+    """torch autograd + torch.optim.AdamW on the host cores, one decoder layer per step."""
+    import torch
+    from oracle import torch_steps as T
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sample = workload_linears("llama3.1-8b-layer")
+    full = workload_linears(args.workload)
+    g = torch.Generator().manual_seed(0)
+    layers = []
+    for _, V, H, _ in sample:
+        w = torch.randn(V, H, generator=g) * 0.02
+        layers.append((T.TorchAdamWLinear(w, HYPER["lr"], (HYPER["beta1"], HYPER["beta2"]), HYPER["eps"], HYPER["weight_decay"]),
+                       torch.randn(BT, H, generator=g).bfloat16(), (torch.randn(BT, V, generator=g) * 1e-2).bfloat16()))
+    steps = max(1, min(args.steps, 20))
+    warmup = max(1, min(args.warmup, 3))
+
+    def one_step():
+        for lin, x, dy in layers:
+            lin.step(x, dy)
+
+    for _ in range(warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    sample_ms = (time.perf_counter() - t0) * 1e3 / steps
+    scale = sum(V * H for _, V, H, _ in full) / sum(V * H for _, V, H, _ in sample)
+    value = sample_ms * scale
+    desc = (f"one decoder layer (7 projections, {sum(V * H for _, V, H, _ in sample) / 1e6:.0f}M parameters), {steps} timed steps "
+            f"at {sample_ms:.0f} ms each, scaled x{scale:.1f} by parameter count to the full workload")
+    print(json.dumps({
+        "impl": "reference", "metric": "fused_wgrad_adamw_ms_per_step", "value": value, "unit": "ms/step",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": value, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "bt": BT, "state": "fp32 W/m/v on the host (torch.optim.AdamW)",
+                   "reference_path": "torch autograd + torch.optim.AdamW on CPU"},
+        "cpu_baseline": {"value": value, "unit": "ms/step", "cores": cores, "kind": "reference", "sample": desc},
+        "e2e": {"value": value, "unit": "ms/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ------------------------------------------------------------------------------------------------
+def run_forge(args):
+    import torch
+    import torch.distributed as dist
+    from forge_b200 import _lib
+    from forge_b200 import kernel as K
+    from forge_b200.tensor_parallel import all_gather_features, feature_range, row_range
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: forge_b200 has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    linears = workload_linears(args.workload)
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+
+    # state: this rank's rows of every weight and moment
+    params = []
+    for name, V, H, grp in linears:
+        r0, r1 = row_range(V, rank, world)
+        w = torch.empty(r1 - r0, H, dtype=torch.bfloat16, device=dev).normal_(0.0, 0.02, generator=gen)
+        m = torch.zeros_like(w)
+        v = torch.zeros_like(w)
+        params.append((name, V, H, grp, r0, r1, w, m, v))
+
+    # activations: one X per distinct in-features (feature shard when N > 1), one dY per distinct V_r
+    x_full, x_shard, dys = {}, {}, {}
+    for name, V, H, grp, r0, r1, *_ in params:
+        if H not in x_full:
+            full = torch.randn(BT, H, device=dev, generator=gen).bfloat16()
+            x_full[H] = full
+            if world > 1:
+                c0, c1 = feature_range(H, rank, world)
+                x_shard[H] = full[:, c0:c1].contiguous()
+        if (r1 - r0) not in dys:
+            dys[r1 - r0] = (torch.randn(BT, r1 - r0, device=dev, generator=gen) * 1e-2).bfloat16()
+
+    # host copies for the end-to-end arm
+    pin = {}
+
+    def pinned(t):
+        key = (tuple(t.shape), t.data_ptr())
+        if key not in pin:
+            pin[key] = t.cpu().pin_memory()
+        return pin[key]
+
+    def step_device(step_no):
+        last_grp, xg = None, None
+        for name, V, H, grp, r0, r1, w, m, v in params:
+            if world > 1:
+                if grp != last_grp:
+                    xg = all_gather_features(x_shard[H])     # NCCL, lands in local memory
+                    last_grp = grp
+                x = xg
+            else:
+                x = x_full[H]
+            K.fused_grad_adamw(dys[r1 - r0], x, w, m, v, step=step_no, **HYPER)
+
+    stage = {}
+
+    def staged(t, tag):
+        key = (tag, tuple(t.shape), t.dtype)
+        if key not in stage:
+            stage[key] = torch.empty_like(t)
+        return stage[key]
+
+    host_result = torch.zeros(2, dtype=torch.float32).pin_memory()
+
+    def step_host(step_no):
+        """Same step, inputs start in pinned host memory; returns H2D / D2H bytes moved."""
+        h2d = 0
+        last_grp, xg = None, None
+        for name, V, H, grp, r0, r1, w, m, v in params:
+            dy_h = pinned(dys[r1 - r0])
+            dy_d = staged(dys[r1 - r0], "dy")
+            dy_d.copy_(dy_h, non_blocking=True)
+            h2d += dy_h.numel() * 2
+            if world > 1:
+                if grp != last_grp:
+                    xs_h = pinned(x_shard[H])
+                    xs_d = staged(x_shard[H], "x")
+                    xs_d.copy_(xs_h, non_blocking=True)
+                    h2d += xs_h.numel() * 2
+                    xg = all_gather_features(xs_d)
+                    last_grp = grp
+                x = xg
+            else:
+                x_h = pinned(x_full[H])
+                x = staged(x_full[H], "x")
+                x.copy_(x_h, non_blocking=True)
+                h2d += x_h.numel() * 2
+            K.fused_grad_adamw(dy_d, x, w, m, v, step=step_no, **HYPER)
+        # the step's result: the device status word and one updated weight, read back to the host
+        host_result[0:1].copy_(_lib.status_word(dev)[0:1].float(), non_blocking=True)
+        host_result[1:2].copy_(params[-1][6][0, 0:1].float(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return h2d, 8
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, first_step):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        extra = None
+        for s in range(steps):
+            extra = fn(first_step + s)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms, extra
+
+    W = max(args.warmup, 3)
+    step_no = 1
+    for _ in range(W):
+        step_device(step_no)
+        step_no += 1
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms_dev, _ = timed(step_device, args.steps, step_no)
+    step_no += args.steps
+
+    step_host(step_no)
+    step_no += 1
+    e2e_steps = max(1, min(args.steps, 5))
+    ms_e2e, moved = timed(step_host, e2e_steps, step_no)
+    step_no += e2e_steps
+    clocks = sampler.stop() if sampler else None
+    status = _lib.read_status(dev)
+
+    peak_gb = torch.cuda.max_memory_allocated(dev) / 1e9
+    if world > 1:
+        t = torch.tensor([peak_gb], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        peak_gb = t.item()
+
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        launches = len(params)
+        # algorithmic bytes this rank moves per step (row shard of the state, full X, dY slice)
+        alg = sum(algorithmic_bytes(r1 - r0, H) for _, V, H, _, r0, r1, *_ in params)
+        achieved = alg / (ms_dev * 1e-3) / 1e9
+        flops = sum(2 * BT * (r1 - r0) * H for _, V, H, _, r0, r1, *_ in params)
+        line = {
+            "metric": "fused_wgrad_adamw_ms_per_step", "value": ms_dev, "unit": "ms/step", "n_gpus": world,
+            "steps": args.steps, "warmup": W, "ms_per_step": ms_dev, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "bt": BT, "linears": launches, "weights": "bf16", "moments": "bf16",
+                       "optimizer": "adamw", "parallelism": f"tp{world}-rows" if world > 1 else "single",
+                       "l2": "each weight and its moments are distinct buffers (45 GB in total), so every launch "
+                             "streams state that is not in L2; no flush needed",
+                       "parameters": sum(V * H for _, V, H, *_ in params)},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
+                         "kernel": "forge_wgrad_kernel<bf16 W, bf16 moments, AdamW>",
+                         "algorithmic_bytes_per_launch": alg / launches, "avg_launch_us": ms_dev * 1e3 / launches,
+                         "tflops": flops / (ms_dev * 1e-3) / 1e12,
+                         # dram read+write per launch from the ncu capture in profiles/, scaled by bytes
+                         "traffic": TRAFFIC_RATIO * alg / launches if TRAFFIC_RATIO else None},
+            "e2e": {"value": ms_e2e, "unit": "ms/step", "h2d_bytes_per_step": moved[0], "d2h_bytes_per_step": moved[1],
+                    "steps": e2e_steps},
+            "gpu_launches": launches * args.steps,
+            "peak_hbm_gb": peak_gb, "device_status": status, "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args.workload)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram bytes (read + write) inside the launches per algorithmic byte, from the ncu capture summarised
+# in profiles/wgrad_adamw_bf16_llama8b_layer_ncu.md (reads equal the algorithmic reads; the writes still
+# dirty in L2 when a launch ends make the in-launch total smaller than the algorithmic one)
+TRAFFIC_RATIO = 0.88
+
+
+def cpu_baseline(workload):
+    """The oracle's torch restatement (torch autograd + torch.optim.AdamW, fp32) on the host cores:
+    one decoder layer, a few steps, scaled by parameter count."""
+    import torch
+    from oracle import torch_steps as T
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sample = workload_linears("llama3.1-8b-layer")
+    full = workload_linears(workload)
+    g = torch.Generator().manual_seed(0)
+    layers = []
+    for _, V, H, _ in sample:
+        layers.append((T.TorchAdamWLinear(torch.randn(V, H, generator=g) * 0.02, HYPER["lr"],
+                                          (HYPER["beta1"], HYPER["beta2"]), HYPER["eps"], HYPER["weight_decay"]),
+                       torch.randn(BT, H, generator=g).bfloat16(), (torch.randn(BT, V, generator=g) * 1e-2).bfloat16()))
+    for lin, x, dy in layers:
+        lin.step(x, dy)
+    steps = 5
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        for lin, x, dy in layers:
+            lin.step(x, dy)
+    sample_ms = (time.perf_counter() - t0) * 1e3 / steps
+    scale = sum(V * H for _, V, H, _ in full) / sum(V * H for _, V, H, _ in sample)
+    return {"value": sample_ms * scale, "unit": "ms/step", "cores": cores, "kind": "port",
+            "sample": f"torch autograd + torch.optim.AdamW (fp32) on one decoder layer's 7 projections, {steps} steps at "
+                      f"{sample_ms:.0f} ms, scaled x{scale:.1f} by parameter count"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="forge", choices=["forge", "reference"])
+    ap.add_argument("--workload", default="llama3.1-8b-linears")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_forge(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,160 @@
+"""Row-sharded tensor parallelism for the fused weight-gradient + optimizer path.
+
+The reference has no distributed code (no ``torch.distributed`` call site anywhere in its tree); this
+mode is new.  It shards every weight along its OUTPUT rows V -- the only axis along which
+``dW[v, :] = sum_bt dY[bt, v] X[bt, :]`` and its optimizer update need no gradient reduction -- so rank
+``r`` of ``R`` owns rows ``[r V/R, (r+1) V/R)`` of W, of the moments and of their per-row scale arrays
+(``row_range``).  Activations travel feature-sharded between linears:
+
+    before a linear   all-gather X          (BT, H/R) per rank -> (BT, H) in local memory  [NCCL]
+    forward           Y_r = X W_r^T         (BT, V/R), stays sharded
+    backward          dW_r = dY_r^T X       local fused kernel, no communication
+                      dX = sum_r dY_r W_r   reduce-scatter over ranks -> (BT, H/R)          [NCCL]
+
+One process per GPU; ``torch.distributed`` (NCCL over NVLink / NVSwitch on GPUs, gloo on CPU for the
+host-logic tests).  A gathered tensor always lands in this rank's own memory before any kernel reads
+it; no kernel of this package dereferences a peer's memory.
+
+Parity: results equal the single-GPU run row for row, because each row's update depends on no other
+row.  The one exception is ``state_mode="fp8"`` (one scale per tensor): each rank keeps the scale
+of its own shard, so codes differ from a single-GPU run; use ``"fp8_block"`` where they must match.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from forge_b200.module import FusedLinear
+
+
+def row_range(V: int, rank: int, world: int) -> tuple[int, int]:
+    """Rows of a (V, H) weight owned by `rank`: contiguous blocks, sizes differing by at most one
+    8-row group so that every shard keeps the 16-byte row-pitch alignment of its dY slice."""
+    if V % 8 != 0:
+        raise ValueError(f"V ({V}) must be a multiple of 8 to be row-sharded")
+    groups = V // 8
+    base, extra = divmod(groups, world)
+    start = rank * base + min(rank, extra)
+    count = base + (1 if rank < extra else 0)
+    return start * 8, (start + count) * 8
+
+
+def feature_range(H: int, rank: int, world: int) -> tuple[int, int]:
+    """Columns of a feature-sharded activation held by `rank` (equal shards; H % world == 0)."""
+    if H % world != 0:
+        raise ValueError(f"feature dimension {H} is not divisible by the world size {world}")
+    s = H // world
+    return rank * s, (rank + 1) * s
+
+
+def all_gather_features(x_shard: torch.Tensor, group=None) -> torch.Tensor:
+    """(…, H/R) per rank -> (…, H) on every rank (feature-concatenated)."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return x_shard
+    x_shard = x_shard.contiguous()
+    lead = x_shard.shape[:-1]
+    flat = torch.empty((world * x_shard.shape[0],) + tuple(x_shard.shape[1:]), dtype=x_shard.dtype,
+                       device=x_shard.device)
+    dist.all_gather_into_tensor(flat, x_shard, group=group)     # rank blocks concatenated along dim 0
+    out = flat.view((world,) + tuple(x_shard.shape))
+    # (R, …, H/R) -> (…, R, H/R) -> (…, H)
+    nd = x_shard.dim()
+    perm = tuple(range(1, nd)) + (0, nd)
+    return out.permute(*perm).reshape(*lead, world * x_shard.shape[-1])
+
+
+def reduce_scatter_features(x_full: torch.Tensor, group=None) -> torch.Tensor:
+    """Sum of the ranks' (…, H) partial results, scattered by feature block: returns (…, H/R)."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return x_full
+    lead = x_full.shape[:-1]
+    H = x_full.shape[-1]
+    s = H // world
+    # (…, R, H/R) -> (R, …, H/R) so that block r is contiguous
+    nd = x_full.dim()
+    blocks = x_full.reshape(*lead, world, s).permute(nd - 1, *range(nd - 1), nd).contiguous()
+    if dist.get_backend(group) == "gloo":
+        # gloo (CPU host-logic tests) has no reduce-scatter: all-reduce and keep this rank's block
+        dist.all_reduce(blocks, op=dist.ReduceOp.SUM, group=group)
+        return blocks[dist.get_rank(group)].clone()
+    out = torch.empty(tuple(lead) + (s,), dtype=x_full.dtype, device=x_full.device)
+    dist.reduce_scatter_tensor(out, blocks.view((world * blocks.shape[1],) + tuple(blocks.shape[2:])),
+                               op=dist.ReduceOp.SUM, group=group)
+    return out
+
+
+class _GatherX(torch.autograd.Function):
+    """all-gather in forward, reduce-scatter of the gradient in backward."""
+
+    @staticmethod
+    def forward(ctx, x_shard, group):
+        ctx.group = group
+        return all_gather_features(x_shard, group)
+
+    @staticmethod
+    def backward(ctx, grad_full):
+        return reduce_scatter_features(grad_full.contiguous(), ctx.group), None
+
+
+class RowShardedFusedLinear(nn.Module):
+    """A ``FusedLinear`` holding only this rank's rows of the weight (and of its optimizer state).
+
+    ``forward`` takes the feature-sharded activation (…, H/R), gathers it, and returns this rank's
+    slice (…, V_r) of the output.  Its backward runs the fused update on the local rows and returns
+    the reduce-scattered input gradient (…, H/R).  With ``gather_input=False`` the caller passes an
+    already gathered (…, H) activation (several linears sharing one gather, e.g. q/k/v or gate/up)
+    and receives the full-width partial dX, to be summed once and reduce-scattered by the caller.
+    """
+
+    def __init__(self, in_features, out_features, rank=None, world=None, group=None, gather_input=True,
+                 dtype=None, device=None, **fused_kwargs):
+        super().__init__()
+        self.group = group
+        self.world = world if world is not None else dist.get_world_size(group)
+        self.rank = rank if rank is not None else dist.get_rank(group)
+        self.in_features, self.out_features = in_features, out_features
+        self.row_start, self.row_end = row_range(out_features, self.rank, self.world)
+        self.gather_input = gather_input
+        self.local = FusedLinear(in_features, self.row_end - self.row_start, **fused_kwargs)
+        if dtype is not None or device is not None:
+            self.local = self.local.to(device=device, dtype=dtype)
+
+    @classmethod
+    def from_full_weight(cls, weight: torch.Tensor, rank=None, world=None, group=None, **kw):
+        """Build from the full (V, H) weight: keeps a copy of this rank's rows only."""
+        V, H = weight.shape
+        m = cls(H, V, rank=rank, world=world, group=group, **kw)
+        with torch.no_grad():
+            m.local.weight.data = weight[m.row_start:m.row_end].detach().clone()
+        return m
+
+    @property
+    def weight(self):
+        return self.local.weight
+
+    def forward(self, x):
+        if self.gather_input and self.world > 1:
+            x = _GatherX.apply(x, self.group)
+        return self.local(x)
+
+    def gather_full_weight(self) -> torch.Tensor:
+        """Reassemble the (V, H) weight on every rank (checkpointing / parity checks)."""
+        return gather_rows(self.local.weight.data, self.out_features, self.rank, self.world, self.group)
+
+
+def gather_rows(shard: torch.Tensor, V: int, rank: int, world: int, group=None) -> torch.Tensor:
+    """All-gather row shards of possibly unequal height into the full (V, …) tensor."""
+    if world == 1:
+        return shard.clone()
+    sizes = [row_range(V, r, world) for r in range(world)]
+    tallest = max(e - s for s, e in sizes)
+    padded = torch.zeros((tallest,) + tuple(shard.shape[1:]), dtype=shard.dtype, device=shard.device)
+    padded[: shard.shape[0]] = shard
+    flat = torch.empty((world * tallest,) + tuple(shard.shape[1:]), dtype=shard.dtype, device=shard.device)
+    dist.all_gather_into_tensor(flat, padded, group=group)
+    out = flat.view((world, tallest) + tuple(shard.shape[1:]))
+    return torch.cat([out[r, : e - s] for r, (s, e) in enumerate(sizes)], dim=0)
