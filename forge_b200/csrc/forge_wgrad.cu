@@ -1,4 +1,5 @@
 // C-ABI entry of the fused weight-gradient + optimizer update: validation, tensor maps, dispatch.
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -38,10 +39,14 @@ struct StateTensors {
   int64_t V, H, ld_w, ld_state;
 };
 
-template <int W_DT, int ST, int OPT>
+template <int W_DT, int ST, int OPT, int CG>
 static int launch_wgrad(const CUtensorMap& tm_dy, const CUtensorMap& tm_x, const StateTensors& t,
-                        const WgradParams& p, int grid, cudaStream_t stream) {
-  using Cfg = WgradCfg<W_DT, ST, OPT>;
+                        WgradParams p, int sm_count, cudaStream_t stream) {
+  using Cfg = WgradCfg<W_DT, ST, OPT, CG>;
+  p.tiles_m = static_cast<int>((t.V + TILE_M * CG - 1) / (TILE_M * CG));
+  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  // one persistent CTA (or CTA pair) per SM (pair of SMs)
+  const int grid = CG * static_cast<int>(std::min<int64_t>(tiles, sm_count / CG));
   // per-warp boxes: 32 rows x (one swizzle row of the chunk)
   CUtensorMap tm_w, tm_m, tm_v;
   int rc;
@@ -49,10 +54,24 @@ static int launch_wgrad(const CUtensorMap& tm_dy, const CUtensorMap& tm_x, const
   if ((rc = encode_tmap_2d(&tm_w, t.W, Cfg::kWES, true, t.V, t.H, t.ld_w, WG::kBoxRowBytes / Cfg::kWES, 32,
                            WG::kSwizzle)) != FORGE_OK)
     return rc;
+  CUtensorMap tl_w, tl_m, tl_v;
+  if ((rc = encode_tmap_2d(&tl_w, t.W, Cfg::kWES, true, t.V, t.H, t.ld_w, WG::kBoxRowBytes / Cfg::kWES, 128,
+                           WG::kSwizzle)) != FORGE_OK)
+    return rc;
   tm_m = tm_w;
   tm_v = tm_w;
+  tl_m = tl_w;
+  tl_v = tl_w;
   if constexpr (Cfg::kNMom > 0) {
     using SG = BoxGeom<Cfg::kSRB>;
+    if ((rc = encode_tmap_2d(&tl_m, t.m, Cfg::kSES, Cfg::kSES != 1, t.V, t.H, t.ld_state,
+                             SG::kBoxRowBytes / Cfg::kSES, 128, SG::kSwizzle)) != FORGE_OK)
+      return rc;
+    if constexpr (Cfg::kNMom > 1) {
+      if ((rc = encode_tmap_2d(&tl_v, t.v, Cfg::kSES, Cfg::kSES != 1, t.V, t.H, t.ld_state,
+                               SG::kBoxRowBytes / Cfg::kSES, 128, SG::kSwizzle)) != FORGE_OK)
+        return rc;
+    }
     if ((rc = encode_tmap_2d(&tm_m, t.m, Cfg::kSES, Cfg::kSES != 1, t.V, t.H, t.ld_state,
                              SG::kBoxRowBytes / Cfg::kSES, 32, SG::kSwizzle)) != FORGE_OK)
       return rc;
@@ -62,7 +81,7 @@ static int launch_wgrad(const CUtensorMap& tm_dy, const CUtensorMap& tm_x, const
         return rc;
     }
   }
-  auto kern = forge_wgrad_kernel<W_DT, ST, OPT>;
+  auto kern = forge_wgrad_kernel<W_DT, ST, OPT, CG>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -73,18 +92,43 @@ static int launch_wgrad(const CUtensorMap& tm_dy, const CUtensorMap& tm_x, const
     attr_set[dev] = true;
   }
   // with no tokens the operand maps are never used; pass valid ones anyway
-  kern<<<grid, NUM_THREADS, Cfg::kSmemBytes, stream>>>(p.num_kb > 0 ? tm_dy : tm_w, p.num_kb > 0 ? tm_x : tm_w,
-                                                       tm_w, tm_m, tm_v, p);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p.num_kb > 0 ? tm_dy : tm_w, p.num_kb > 0 ? tm_x : tm_w, tm_w, tm_m,
+                                     tm_v, tl_w, tl_m, tl_v, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "wgrad kernel launch: %s", cudaGetErrorString(e));
   return FORGE_OK;
 }
 
+// CTA pairs are used whenever the weight has more than one 128-row tile; FORGE_CTA_PAIRS=0 in the
+// environment keeps single CTAs (a tuning / bisecting aid, read once).
+static bool pairs_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("FORGE_CTA_PAIRS");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
 template <int W_DT>
 static int dispatch_wgrad(int opt, int st, const CUtensorMap& a, const CUtensorMap& b, const StateTensors& t,
-                          const WgradParams& p, int grid, cudaStream_t s) {
-#define FORGE_CASE(OPT_, ST_) \
-  if (opt == OPT_ && st == ST_) return launch_wgrad<W_DT, ST_, OPT_>(a, b, t, p, grid, s);
+                          const WgradParams& p, int sm_count, cudaStream_t s) {
+  const bool pair = pairs_enabled() && t.V > TILE_M && sm_count >= 2;
+#define FORGE_CASE(OPT_, ST_)                                                             \
+  if (opt == OPT_ && st == ST_)                                                           \
+    return pair ? launch_wgrad<W_DT, ST_, OPT_, 2>(a, b, t, p, sm_count, s)               \
+                : launch_wgrad<W_DT, ST_, OPT_, 1>(a, b, t, p, sm_count, s);
   FORGE_CASE(OPT_ADAMW, ST_BF16)
   FORGE_CASE(OPT_ADAMW, ST_F32)
   FORGE_CASE(OPT_ADAMW, ST_INT8)
@@ -188,7 +232,7 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
   p.V = static_cast<int>(a.V);
   p.H = static_cast<int>(a.H);
   p.num_kb = static_cast<int>((bt + OP_BK - 1) / OP_BK);
-  p.tiles_m = static_cast<int>((a.V + TILE_M - 1) / TILE_M);
+  p.tiles_m = 0;  // set by the launcher (depends on single CTAs vs CTA pairs)
   p.tiles_n = static_cast<int>((a.H + TILE_N - 1) / TILE_N);
   p.hyper = make_hyper(a.hyper);
   p.m_scale = a.state.m_scale;
@@ -197,9 +241,6 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
   p.m_absmax = a.state.m_absmax_next;
   p.v_absmax = a.state.v_absmax_next;
   p.status = a.status;
-  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
-  const int grid = static_cast<int>(std::min<int64_t>(tiles, di->sm_count));
-
-  if (a.w_dtype == FORGE_DT_BF16) return dispatch_wgrad<DT_BF16>(opt, st, tm_dy, tm_x, t, p, grid, stream);
-  return dispatch_wgrad<DT_F32>(opt, st, tm_dy, tm_x, t, p, grid, stream);
+  if (a.w_dtype == FORGE_DT_BF16) return dispatch_wgrad<DT_BF16>(opt, st, tm_dy, tm_x, t, p, di->sm_count, stream);
+  return dispatch_wgrad<DT_F32>(opt, st, tm_dy, tm_x, t, p, di->sm_count, stream);
 }

@@ -197,14 +197,17 @@ __host__ __device__ constexpr int state_stage_bytes(int wes, int ses, int nmom, 
   return 128 * cn * (wes + nmom * ses);
 }
 
-template <int W_DT, int ST, int OPT>
+// CG = 1: one CTA per 128 x 256 tile.  CG = 2: a pair of CTAs (cluster of two, tcgen05 cta_group::2)
+// per 256 x 256 tile; each CTA owns 128 rows and stages only HALF of the X panel (the pair MMA reads
+// both halves), which cuts the L2 -> SM panel traffic per output by a third.
+template <int W_DT, int ST, int OPT, int CG = 1>
 struct WgradCfg {
   static constexpr int kWES = (W_DT == DT_BF16) ? 2 : 4;
   static constexpr int kNMom = num_moments(OPT);
   static constexpr int kSES = state_elem_size(ST);
   static constexpr int kBK = OP_BK;
-  static constexpr int kNStage = OP_STAGES;
-  static constexpr int kOpStageBytes = (TILE_M + TILE_N) * kBK * 2;
+  static constexpr int kNStage = (CG == 2) ? OP_STAGES + 2 : OP_STAGES;
+  static constexpr int kOpStageBytes = (TILE_M + TILE_N / CG) * kBK * 2;
   static constexpr int kCtrlBytes = 1024;
   static constexpr int kRoom = SMEM_BUDGET - kCtrlBytes - 1024 - kNStage * kOpStageBytes;
   // 64-column chunks when four such stages fit (always with one-byte codes, whose quantisation block
@@ -236,12 +239,16 @@ struct alignas(8) CtrlBlock {
 };
 
 // ------------------------------------------------------------------------------------------------
-template <int W_DT, int ST, int OPT>
+template <int W_DT, int ST, int OPT, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_x,
                    const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_m,
-                   const __grid_constant__ CUtensorMap tm_v, const WgradParams p) {
-  using Cfg = WgradCfg<W_DT, ST, OPT>;
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tl_w,
+                   const __grid_constant__ CUtensorMap tl_m, const __grid_constant__ CUtensorMap tl_v,
+                   const WgradParams p) {
+  // tm_w/m/v: store maps, boxes of 32 rows (one per epilogue warp); tl_w/m/v: load maps over the same
+  // tensors with boxes of 128 rows (one TMA instruction per tensor and chunk)
+  using Cfg = WgradCfg<W_DT, ST, OPT, CG>;
   constexpr int BK = Cfg::kBK;
   constexpr int NSTAGE = Cfg::kNStage;
   constexpr int NSS = Cfg::kNSS;
@@ -256,7 +263,8 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
   constexpr int WBC = BoxGeom<WRB>::kBoxRowBytes / WES;                 // columns per W box
   constexpr int SBC = (NMOM > 0) ? BoxGeom<SRB>::kBoxRowBytes / (SES > 0 ? SES : 1) : 1;
   constexpr int A_BYTES = TILE_M * BK * 2;
-  constexpr int B_BYTES = TILE_N * BK * 2;
+  constexpr int B_COLS = TILE_N / CG;      // columns of the X panel this CTA stages
+  constexpr int B_BYTES = B_COLS * BK * 2;
   constexpr int SLAB_BYTES = 64 * BK * 2;  // one 64-element M/N slab of a K panel
 
   extern __shared__ uint8_t smem_raw[];
@@ -271,28 +279,40 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
   const int lane = threadIdx.x & 31;
   volatile int* abort_word = &ctrl->abort_word;
 
+  // pair mode: rank 0 of the cluster is the leader (issues the MMAs, owns op_full and acc_empty)
+  const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const int first_tile = (CG == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int tile_stride = (CG == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSTAGE; ++i) { mbar_init(&ctrl->op_full[i], 1); mbar_init(&ctrl->op_empty[i], 1); }
     for (int i = 0; i < NSS; ++i) { mbar_init(&ctrl->st_full[i], 1); mbar_init(&ctrl->st_empty[i], 4); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&ctrl->acc_full[i], 1); mbar_init(&ctrl->acc_empty[i], NUM_EPI_WARPS); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&ctrl->acc_full[i], 1); mbar_init(&ctrl->acc_empty[i], NUM_EPI_WARPS * CG); }
     ctrl->abort_word = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(&ctrl->tmem_base, TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (CG == 2) {
+      tmem_alloc_pair(&ctrl->tmem_base, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&ctrl->tmem_base, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   if (warp == 0 && lane == 0) { prefetch_tmap(&tm_dy); prefetch_tmap(&tm_x); }
   if (warp == 2 && lane == 0) {
-    prefetch_tmap(&tm_w);
-    if (NMOM > 0) prefetch_tmap(&tm_m);
-    if (NMOM > 1) prefetch_tmap(&tm_v);
+    prefetch_tmap(&tl_w);
+    if (NMOM > 0) prefetch_tmap(&tl_m);
+    if (NMOM > 1) prefetch_tmap(&tl_v);
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();   // the peer's barriers exist before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
 
+  // p.tiles_m counts row tiles of TILE_M * CG rows; both CTAs of a pair walk the same tile list
   const int num_tiles = p.tiles_m * p.tiles_n;
 
   if (warp == 0) {
@@ -300,8 +320,8 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
     if (lane == 0) {
       const uint64_t pol = policy_evict_last();
       uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int row0 = (tile / p.tiles_n) * TILE_M;
+      for (int tile = first_tile; tile < num_tiles; tile += tile_stride) {
+        const int row0 = (tile / p.tiles_n) * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
         const int col0 = (tile % p.tiles_n) * TILE_N;
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           const int s = it % NSTAGE;
@@ -309,23 +329,36 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           if (!mbar_wait(&ctrl->op_empty[s], ph ^ 1, abort_word, ERR_WAIT_OP_EMPTY)) goto done;
           uint8_t* a = op_buf + s * Cfg::kOpStageBytes;
           uint8_t* b = a + A_BYTES;
-          mbar_expect_tx(&ctrl->op_full[s], A_BYTES + B_BYTES);
+          if constexpr (CG == 2) {
+            // both CTAs' copies count on the LEADER's barrier; the leader expects the bytes of both
+            const uint32_t full_leader = map_to_cta(smem_u32(&ctrl->op_full[s]), 0);
+            if (cta_rank == 0) mbar_expect_tx(&ctrl->op_full[s], 2 * (A_BYTES + B_BYTES));
+            const int bcol0 = col0 + static_cast<int>(cta_rank) * B_COLS;
 #pragma unroll
-          for (int i = 0; i < TILE_M / 64; ++i)
-            tma_load_2d(a + i * SLAB_BYTES, &tm_dy, &ctrl->op_full[s], row0 + 64 * i, kb * BK, pol);
+            for (int i = 0; i < TILE_M / 64; ++i)
+              tma_load_2d_pair(a + i * SLAB_BYTES, &tm_dy, full_leader, row0 + 64 * i, kb * BK, pol);
 #pragma unroll
-          for (int i = 0; i < TILE_N / 64; ++i)
-            tma_load_2d(b + i * SLAB_BYTES, &tm_x, &ctrl->op_full[s], col0 + 64 * i, kb * BK, pol);
+            for (int i = 0; i < B_COLS / 64; ++i)
+              tma_load_2d_pair(b + i * SLAB_BYTES, &tm_x, full_leader, bcol0 + 64 * i, kb * BK, pol);
+          } else {
+            mbar_expect_tx(&ctrl->op_full[s], A_BYTES + B_BYTES);
+#pragma unroll
+            for (int i = 0; i < TILE_M / 64; ++i)
+              tma_load_2d(a + i * SLAB_BYTES, &tm_dy, &ctrl->op_full[s], row0 + 64 * i, kb * BK, pol);
+#pragma unroll
+            for (int i = 0; i < TILE_N / 64; ++i)
+              tma_load_2d(b + i * SLAB_BYTES, &tm_x, &ctrl->op_full[s], col0 + 64 * i, kb * BK, pol);
+          }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(TILE_M, TILE_N, true, true);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(TILE_M * CG, TILE_N, true, true);
       uint32_t it = 0;
       uint32_t tile_it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_it) {
+      for (int tile = first_tile; tile < num_tiles; tile += tile_stride, ++tile_it) {
         const int buf = tile_it & 1;
         const uint32_t aph = (tile_it >> 1) & 1;
         if (!mbar_wait(&ctrl->acc_empty[buf], aph ^ 1, abort_word, ERR_WAIT_ACC_EMPTY)) goto done;
@@ -343,11 +376,15 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             // advancing K by 16 rows = two 1024-byte swizzle atoms
             const uint64_t da = make_smem_desc_sw128(a_addr + k * (UMMA_K * 128), SLAB_BYTES, 1024);
             const uint64_t db = make_smem_desc_sw128(b_addr + k * (UMMA_K * 128), SLAB_BYTES, 1024);
-            umma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if constexpr (CG == 2) umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else umma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&ctrl->op_empty[s]);
+          // frees the stage in both CTAs of a pair
+          if constexpr (CG == 2) umma_commit_pair(&ctrl->op_empty[s], 3);
+          else umma_commit(&ctrl->op_empty[s]);
         }
-        umma_commit(&ctrl->acc_full[buf]);
+        if constexpr (CG == 2) umma_commit_pair(&ctrl->acc_full[buf], 3);
+        else umma_commit(&ctrl->acc_full[buf]);
       }
     }
   } else if (warp == 2) {
@@ -359,8 +396,8 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
       // 126 us on a 14336 x 4096 bf16 update when this policy was changed).
       const uint64_t pol = policy_evict_normal();
       uint32_t q = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int row0 = (tile / p.tiles_n) * TILE_M;
+      for (int tile = first_tile; tile < num_tiles; tile += tile_stride) {
+        const int row0 = (tile / p.tiles_n) * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
         const int col0 = (tile % p.tiles_n) * TILE_N;
         for (int c = 0; c < NCH; ++c, ++q) {
           const int s = q % NSS;
@@ -370,26 +407,19 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           mbar_expect_tx(&ctrl->st_full[s], Cfg::kStageBytes);
           const int cc = col0 + c * CN;
 #pragma unroll
-          for (int rb = 0; rb < 4; ++rb) {
-            const int rr = row0 + 32 * rb;
+          for (int bx = 0; bx < BoxGeom<WRB>::kBoxes; ++bx)
+            tma_load_2d(wb + bx * BoxGeom<WRB>::kBoxBytes, &tl_w, &ctrl->st_full[s], cc + bx * WBC, row0, pol);
+          if constexpr (NMOM > 0) {
+            uint8_t* mb = wb + Cfg::kWBytes;
 #pragma unroll
-            for (int bx = 0; bx < BoxGeom<WRB>::kBoxes; ++bx)
-              tma_load_2d(wb + bx * BoxGeom<WRB>::kBoxBytes + rb * 32 * BoxGeom<WRB>::kPitch, &tm_w,
-                          &ctrl->st_full[s], cc + bx * WBC, rr, pol);
-            if constexpr (NMOM > 0) {
-              uint8_t* mb = wb + Cfg::kWBytes;
+            for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
+              tma_load_2d(mb + bx * BoxGeom<SRB>::kBoxBytes, &tl_m, &ctrl->st_full[s], cc + bx * SBC, row0, pol);
+          }
+          if constexpr (NMOM > 1) {
+            uint8_t* vb = wb + Cfg::kWBytes + Cfg::kSBytes;
 #pragma unroll
-              for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-                tma_load_2d(mb + bx * BoxGeom<SRB>::kBoxBytes + rb * 32 * BoxGeom<SRB>::kPitch, &tm_m,
-                            &ctrl->st_full[s], cc + bx * SBC, rr, pol);
-            }
-            if constexpr (NMOM > 1) {
-              uint8_t* vb = wb + Cfg::kWBytes + Cfg::kSBytes;
-#pragma unroll
-              for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-                tma_load_2d(vb + bx * BoxGeom<SRB>::kBoxBytes + rb * 32 * BoxGeom<SRB>::kPitch, &tm_v,
-                            &ctrl->st_full[s], cc + bx * SBC, rr, pol);
-            }
+            for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
+              tma_load_2d(vb + bx * BoxGeom<SRB>::kBoxBytes, &tl_v, &ctrl->st_full[s], cc + bx * SBC, row0, pol);
           }
         }
       }
@@ -425,8 +455,8 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
         held_stage = -1;
       }
     };
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
-      const int row0 = (tile / p.tiles_n) * TILE_M;
+    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride, ++tile_it) {
+      const int row0 = (tile / p.tiles_n) * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
       const int col0 = (tile % p.tiles_n) * TILE_N;
       const int buf = tile_it & 1;
       const uint32_t aph = (tile_it >> 1) & 1;
@@ -689,7 +719,10 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
       // all tcgen05.ld of this warp for this accumulator have completed
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ctrl->acc_empty[buf]);
+      if (lane == 0) {
+        if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&ctrl->acc_empty[buf]), 0));
+        else mbar_arrive(&ctrl->acc_empty[buf]);
+      }
     }
     release_held();
     if (lane == 0) tma_store_wait_all<0>();
@@ -718,9 +751,12 @@ done:
     if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
     __syncthreads();
   }
+  // a pair leaves together: the peer's shared memory and barriers stay valid until both are done
+  if constexpr (CG == 2) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 

@@ -72,37 +72,63 @@ def _state(mode=ST_NONE, m=None, v=None, m_scale=None, v_scale=None, m_absmax=No
     return st
 
 
+# Marshalled argument blocks are cached per weight: W / moment pointers, shapes and dtypes do not change
+# between steps, so a call only refreshes the activation pointers, the token count, the hyper-parameters
+# and the stream.  (225 launches per Llama-8B step: the per-call host cost matters once the GPU time per
+# launch drops below ~50 us, e.g. in the row-sharded mode.)
+_wgrad_cache: dict[tuple, ForgeWgradArgs] = {}
+_WGRAD_CACHE_MAX = 4096
+
+
 def _wgrad(grad_output, input, weight, optimizer, state, hyper):
-    _require_cuda(grad_output, input, weight)
+    if not (grad_output.is_cuda and input.is_cuda and weight.is_cuda):
+        _require_cuda(grad_output, input, weight)
     assert grad_output.is_contiguous() and input.is_contiguous()
-    _row_major_2d(weight, "weight")
     BT, V = grad_output.shape
     H = input.shape[1]
-    if input.shape[0] != BT or tuple(weight.shape) != (V, H):
+    odt = grad_output.dtype
+    key = (weight.data_ptr(), state.m, state.v, state.m_scale, optimizer, state.mode, V, H, weight.stride(0),
+           weight.dtype, odt)
+    a = _wgrad_cache.get(key)
+    lib = _lib.load()
+    if a is None:
+        _row_major_2d(weight, "weight")
+        if input.shape[0] != BT or tuple(weight.shape) != (V, H):
+            raise ValueError(f"shape mismatch: grad_output {tuple(grad_output.shape)}, input {tuple(input.shape)}, "
+                             f"weight {tuple(weight.shape)}")
+        if odt != input.dtype:
+            raise ValueError("grad_output and input must have the same dtype")
+        a = ForgeWgradArgs()
+        a.W = weight.data_ptr()
+        a.V, a.H = V, H
+        a.ld_dy, a.ld_x, a.ld_w = V, H, weight.stride(0)
+        a.operand_dtype = _lib.dtype_id(odt)
+        a.w_dtype = _lib.dtype_id(weight.dtype)
+        a.optimizer = optimizer
+        a.flags = 0
+        a.status = _lib.status_word(weight.device).data_ptr()
+        if len(_wgrad_cache) >= _WGRAD_CACHE_MAX:
+            _wgrad_cache.clear()
+        _wgrad_cache[key] = a
+    elif input.shape[0] != BT or weight.shape[0] != V or weight.shape[1] != H or input.dtype != odt:
         raise ValueError(f"shape mismatch: grad_output {tuple(grad_output.shape)}, input {tuple(input.shape)}, "
                          f"weight {tuple(weight.shape)}")
-    if grad_output.dtype != input.dtype:
-        raise ValueError("grad_output and input must have the same dtype")
-    lib = _lib.load()
-    a = ForgeWgradArgs()
-    a.dY, a.X, a.W = grad_output.data_ptr(), input.data_ptr(), weight.data_ptr()
-    a.BT, a.V, a.H = BT, V, H
-    a.ld_dy, a.ld_x, a.ld_w = grad_output.stride(0), input.stride(0), weight.stride(0)
-    a.operand_dtype = _lib.dtype_id(grad_output.dtype)
-    a.w_dtype = _lib.dtype_id(weight.dtype)
-    a.optimizer = optimizer
-    a.flags = 0
+    a.dY, a.X, a.BT = grad_output.data_ptr(), input.data_ptr(), BT
     a.state = state
     a.hyper = hyper
-    nbytes = lib.forge_wgrad_scratch_bytes(BT, V, H, a.operand_dtype)
     scratch = None
-    if nbytes:
+    if odt != torch.bfloat16:
+        nbytes = lib.forge_wgrad_scratch_bytes(BT, V, H, a.operand_dtype)
         scratch = _get_scratch(weight.device, nbytes)
         a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
-    a.status = _lib.status_word(weight.device).data_ptr()
-    with torch.cuda.device(weight.device):
-        rc = lib.forge_wgrad_update(ctypes.byref(a), _lib.current_stream_ptr(weight.device))
-    _lib.check(rc, "forge_wgrad_update")
+    dev = weight.device
+    if dev.index == torch.cuda.current_device():
+        rc = lib.forge_wgrad_update(ctypes.byref(a), torch.cuda.current_stream().cuda_stream)
+    else:
+        with torch.cuda.device(dev):
+            rc = lib.forge_wgrad_update(ctypes.byref(a), _lib.current_stream_ptr(dev))
+    if rc:
+        _lib.check(rc, "forge_wgrad_update")
 
 
 def _optim(grad, weight, optimizer, state, hyper):
