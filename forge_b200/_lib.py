@@ -108,6 +108,7 @@ class ForgeOptimArgs(ctypes.Structure):
 # every symbol include/forge_b200.h declares, with its ctypes signature
 _SIGNATURES = {
     "forge_wgrad_update": (ctypes.c_int, [ctypes.POINTER(ForgeWgradArgs), ctypes.c_void_p]),
+    "forge_wgrad_update_static_scratch": (ctypes.c_int, [ctypes.POINTER(ForgeWgradArgs), ctypes.c_void_p]),
     "forge_wgrad_scratch_bytes": (ctypes.c_size_t, [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32]),
     "forge_optimizer_update": (ctypes.c_int, [ctypes.POINTER(ForgeOptimArgs), ctypes.c_void_p]),
     "forge_fp8_prestep": (ctypes.c_int, [ctypes.c_void_p] * 5),

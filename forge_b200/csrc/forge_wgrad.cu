@@ -244,3 +244,59 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
   if (a.w_dtype == FORGE_DT_BF16) return dispatch_wgrad<DT_BF16>(opt, st, tm_dy, tm_x, t, p, di->sm_count, stream);
   return dispatch_wgrad<DT_F32>(opt, st, tm_dy, tm_x, t, p, di->sm_count, stream);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant for fp32 operands.
+//
+// The fp32-operand path needs scratch for the bf16 hi/lo split of dY and X.  Some callers have no
+// way to provide it: a plug-in invoked from inside a host framework's allocator callback (calling
+// back into the allocator would re-enter it), or a job whose device memory was committed in full to
+// a static plan at start-up.  For them the scratch is this fixed array inside the library image.
+// Every GPU that loads the library carries it until the process exits.  All calls on a device share
+// it and it keeps whatever the last call wrote; the split kernels overwrite every byte a call will
+// read (padding rows included), so nothing needs clearing, but two calls that overlap on the GPU
+// (different streams) race on it.
+// ------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[FORGE_STATIC_SCRATCH_BYTES];
+
+// Device address of the array on the current device.  The symbol's name is only a host-side handle;
+// the address a kernel can use comes from cudaGetSymbolAddress, asked once per device (and once per
+// calling thread, which also makes sure that thread has the device's context bound).
+static int static_scratch_address(void** out) {
+  static void* cached[64] = {};
+  static thread_local bool thread_ready[64] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64)
+    return fail(FORGE_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (cached[dev] == nullptr || !thread_ready[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(FORGE_ERR_CUDA, "cudaGetSymbolAddress(static scratch) on device %d: %s", dev, cudaGetErrorString(e));
+    cached[dev] = ptr;
+    thread_ready[dev] = true;
+  }
+  *out = cached[dev];
+  return FORGE_OK;
+}
+
+extern "C" int forge_wgrad_update_static_scratch(const ForgeWgradArgs* args, void* cuda_stream) {
+  if (args == nullptr) return fail(FORGE_ERR_INVALID_ARG, "forge_wgrad_update_static_scratch: args is NULL");
+  if (args->operand_dtype != FORGE_DT_F32)
+    return fail(FORGE_ERR_INVALID_ARG, "forge_wgrad_update_static_scratch is for fp32 dY / X; bf16 operands need no "
+                                       "scratch, call forge_wgrad_update");
+  const size_t need = forge_wgrad_scratch_bytes(args->BT, args->V, args->H, FORGE_DT_F32);
+  if (need > static_cast<size_t>(FORGE_STATIC_SCRATCH_BYTES))
+    return fail(FORGE_ERR_SCRATCH,
+                "problem needs %zu bytes of scratch but the built-in array holds %zu: 3 * roundup(BT, 64) * (V + H) * 2 "
+                "must not exceed it; use forge_wgrad_update with caller scratch",
+                need, static_cast<size_t>(FORGE_STATIC_SCRATCH_BYTES));
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != FORGE_OK) return rc;
+  ForgeWgradArgs a = *args;
+  a.scratch = scratch;
+  a.scratch_bytes = static_cast<size_t>(FORGE_STATIC_SCRATCH_BYTES);
+  return forge_wgrad_update(&a, cuda_stream);
+}

@@ -112,6 +112,26 @@ int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream);
  * operands are split into bf16 high/low parts in scratch before the GEMM). */
 size_t forge_wgrad_scratch_bytes(int64_t BT, int64_t V, int64_t H, int32_t operand_dtype);
 
+/* Size of the scratch array built into the library for forge_wgrad_update_static_scratch. */
+#define FORGE_STATIC_SCRATCH_BYTES (32u << 20)
+
+/* forge_wgrad_update for fp32 dY / X without any caller-provided scratch and without a single
+ * allocation: the bf16 hi/lo split goes to a fixed FORGE_STATIC_SCRATCH_BYTES array inside the
+ * library (args->scratch and args->scratch_bytes are ignored).  This entry point has no counterpart
+ * in the reference.  It exists for callers that cannot allocate device memory where they call it
+ * from: a plug-in running inside a host framework's allocator callback, or a job whose memory was
+ * handed out in full to a static plan at start-up.
+ *   - Limit: forge_wgrad_scratch_bytes(BT, V, H, FORGE_DT_F32) = 3 * roundup(BT, 64) * (V + H) * 2
+ *     must not exceed FORGE_STATIC_SCRATCH_BYTES (e.g. BT = 512 with V + H <= 10922); larger problems
+ *     return FORGE_ERR_SCRATCH.  bf16 operands return FORGE_ERR_INVALID_ARG (they need no scratch).
+ *   - The first call on each device (and from each new thread) looks up the array's device address;
+ *     make that first call before starting a stream capture.
+ *   - Each GPU that loads the library holds the array until the process ends.  All calls on a device
+ *     share it and it keeps the previous call's contents; every byte a call reads is written by that
+ *     call first, but calls that overlap on the GPU (two streams) race on it -- serialise them.
+ * Results are identical to forge_wgrad_update given the same arguments. */
+int forge_wgrad_update_static_scratch(const ForgeWgradArgs* args, void* cuda_stream);
+
 /* Arguments of the optimizer-only update on a materialised gradient. */
 typedef struct ForgeOptimArgs {
   const void* grad;  /* (V, H) row-major gradient                                                */
