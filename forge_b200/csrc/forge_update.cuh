@@ -117,6 +117,40 @@ __device__ __forceinline__ int int8_code(float x, float scale, float rscale) {
   const float q = rintf(div_by_rcp(x, scale, rscale));
   return static_cast<int>(fminf(fmaxf(q, -127.0f), 127.0f));
 }
+// Same code in one instruction: round-to-nearest-even conversion with saturation.  The saturation
+// bound of the instruction is [-128, 127]; -128 cannot occur because scale > absmax / 127 keeps
+// |x / scale| < 127.5, so the result equals clamp(rint(x / scale), -127, 127).
+__device__ __forceinline__ uint32_t int8_code_bits(float x, float scale, float rscale) {
+  int32_t q;
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(div_by_rcp(x, scale, rscale)));
+  return static_cast<uint32_t>(q) & 0xFFu;
+}
+// two e4m3 codes at once (round to nearest even, saturate to +-448): low byte = lo, next byte = hi
+__device__ __forceinline__ uint32_t e4m3x2_code_bits(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return static_cast<uint32_t>(r);
+}
+// two e4m3 codes -> two floats
+__device__ __forceinline__ void e4m3x2_to_float(uint32_t two_codes, float& lo, float& hi) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(two_codes)));
+  const __half2 hh = *reinterpret_cast<const __half2*>(&h2);
+  lo = __low2float(hh);
+  hi = __high2float(hh);
+}
+__device__ __forceinline__ uint32_t e5m2x2_code_bits(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return static_cast<uint32_t>(r);
+}
+__device__ __forceinline__ void e5m2x2_to_float(uint32_t two_codes, float& lo, float& hi) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(two_codes)));
+  const __half2 hh = *reinterpret_cast<const __half2*>(&h2);
+  lo = __low2float(hh);
+  hi = __high2float(hh);
+}
 // e4m3 per-block: scale = absmax / 448 + 1e-12 ; code = e4m3_rne(clamp(x / scale, +-448))
 __device__ __forceinline__ float fp8blk_scale(float absmax) {
   return f_add(f_div(absmax, 448.0f), 1e-12f);

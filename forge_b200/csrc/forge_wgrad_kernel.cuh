@@ -573,9 +573,13 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             if (g == 0) release_held();
           }
         } else if constexpr (ST == ST_INT8 || ST == ST_FP8_BLOCK) {
-          // pass 1: dequantise, update W, find the block absmax of the new moments
+          // The 64-column quantisation block is this thread's whole chunk row.  Pass 1 dequantises,
+          // updates W and keeps the new moments in registers (they replace the accumulator values
+          // they were computed from) while tracking the block absmax; pass 2 requantises them with
+          // the new scale.  No shuffles, no recomputation.
           const float sm_old = (i == 0) ? sc_m[0] : sc_m[1];
           const float sv_old = (i == 0) ? sc_v[0] : sc_v[1];
+          float mm[CN], vv[CN];
           float am = 0.0f, av = 0.0f;
 #pragma unroll
           for (int g = 0; g < NG; ++g) {
@@ -585,20 +589,29 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             ld16_bytes(mb, r, g, mq);
             ld16_bytes(vb, r, g, vq);
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              const uint32_t mbits = (mq[k >> 2] >> (8 * (k & 3))) & 0xFFu;
-              const uint32_t vbits = (vq[k >> 2] >> (8 * (k & 3))) & 0xFFu;
-              float m, v;
+            for (int k = 0; k < 16; k += 2) {
+              float m0, m1, v0, v1;
               if constexpr (ST == ST_INT8) {
-                m = f_mul(static_cast<float>(static_cast<int>(static_cast<int8_t>(mbits))), sm_old);
-                v = fmaxf(f_mul(static_cast<float>(static_cast<int>(static_cast<int8_t>(vbits))), sv_old), 1e-8f);
+                m0 = static_cast<float>(static_cast<int>(static_cast<int8_t>(mq[k >> 2] >> (8 * (k & 3)))));
+                m1 = static_cast<float>(static_cast<int>(static_cast<int8_t>(mq[k >> 2] >> (8 * ((k + 1) & 3)))));
+                v0 = static_cast<float>(static_cast<int>(static_cast<int8_t>(vq[k >> 2] >> (8 * (k & 3)))));
+                v1 = static_cast<float>(static_cast<int>(static_cast<int8_t>(vq[k >> 2] >> (8 * ((k + 1) & 3)))));
               } else {
-                m = f_mul(e4m3_to_float(static_cast<uint8_t>(mbits)), sm_old);
-                v = fmaxf(f_mul(e4m3_to_float(static_cast<uint8_t>(vbits)), sv_old), 1e-8f);
+                e4m3x2_to_float(mq[k >> 2] >> (8 * (k & 3)), m0, m1);
+                e4m3x2_to_float(vq[k >> 2] >> (8 * (k & 3)), v0, v1);
               }
-              w[k] = adamw_update(w[k], __uint_as_float(acc[16 * g + k]), m, v, hy);
-              am = fmaxf(am, fabsf(m));
-              av = fmaxf(av, fabsf(v));
+              m0 = f_mul(m0, sm_old);
+              m1 = f_mul(m1, sm_old);
+              v0 = fmaxf(f_mul(v0, sv_old), 1e-8f);
+              v1 = fmaxf(f_mul(v1, sv_old), 1e-8f);
+              w[k] = adamw_update(w[k], __uint_as_float(acc[16 * g + k]), m0, v0, hy);
+              w[k + 1] = adamw_update(w[k + 1], __uint_as_float(acc[16 * g + k + 1]), m1, v1, hy);
+              mm[16 * g + k] = m0;
+              mm[16 * g + k + 1] = m1;
+              vv[16 * g + k] = v0;
+              vv[16 * g + k + 1] = v1;
+              am = fmaxf(am, fmaxf(fabsf(m0), fabsf(m1)));
+              av = fmaxf(av, fmaxf(fabsf(v0), fabsf(v1)));
             }
             store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
             if (g == 0) release_held();
@@ -606,34 +619,19 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           const float sm_new = (ST == ST_INT8) ? int8_scale(am) : fp8blk_scale(am);
           const float sv_new = (ST == ST_INT8) ? int8_scale(av) : fp8blk_scale(av);
           const float rsm = f_div(1.0f, sm_new), rsv = f_div(1.0f, sv_new);
-          // pass 2: recompute the new moments (same instruction sequence) and requantise
 #pragma unroll
           for (int g = 0; g < NG; ++g) {
-            uint32_t mq[4], vq[4], mo[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
-            ld16_bytes(mb, r, g, mq);
-            ld16_bytes(vb, r, g, vq);
+            uint32_t mo[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              const uint32_t mbits = (mq[k >> 2] >> (8 * (k & 3))) & 0xFFu;
-              const uint32_t vbits = (vq[k >> 2] >> (8 * (k & 3))) & 0xFFu;
-              const float gr = __uint_as_float(acc[16 * g + k]);
-              float m, v;
-              if constexpr (ST == ST_INT8) {
-                m = f_mul(static_cast<float>(static_cast<int>(static_cast<int8_t>(mbits))), sm_old);
-                v = fmaxf(f_mul(static_cast<float>(static_cast<int>(static_cast<int8_t>(vbits))), sv_old), 1e-8f);
-              } else {
-                m = f_mul(e4m3_to_float(static_cast<uint8_t>(mbits)), sm_old);
-                v = fmaxf(f_mul(e4m3_to_float(static_cast<uint8_t>(vbits)), sv_old), 1e-8f);
-              }
-              m = f_add(f_mul(hy.beta1, m), f_mul(hy.one_m_beta1, gr));
-              v = f_add(f_mul(hy.beta2, v), f_mul(f_mul(hy.one_m_beta2, gr), gr));
+            for (int k = 0; k < 16; k += 2) {
               uint32_t mc, vc;
               if constexpr (ST == ST_INT8) {
-                mc = static_cast<uint32_t>(int8_code(m, sm_new, rsm)) & 0xFFu;
-                vc = static_cast<uint32_t>(int8_code(v, sv_new, rsv)) & 0xFFu;
+                mc = int8_code_bits(mm[16 * g + k], sm_new, rsm) | (int8_code_bits(mm[16 * g + k + 1], sm_new, rsm) << 8);
+                vc = int8_code_bits(vv[16 * g + k], sv_new, rsv) | (int8_code_bits(vv[16 * g + k + 1], sv_new, rsv) << 8);
               } else {
-                mc = e4m3_code(div_by_rcp(m, sm_new, rsm));
-                vc = e4m3_code(div_by_rcp(v, sv_new, rsv));
+                // |x / scale| < 448.5 by construction of the scale, and the conversion saturates
+                mc = e4m3x2_code_bits(div_by_rcp(mm[16 * g + k], sm_new, rsm), div_by_rcp(mm[16 * g + k + 1], sm_new, rsm));
+                vc = e4m3x2_code_bits(div_by_rcp(vv[16 * g + k], sv_new, rsv), div_by_rcp(vv[16 * g + k + 1], sv_new, rsv));
               }
               mo[k >> 2] |= mc << (8 * (k & 3));
               vo[k >> 2] |= vc << (8 * (k & 3));
@@ -657,18 +655,23 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             ld16_bytes(mb, r, g, mq);
             ld16_bytes(vb, r, g, vq);
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              const uint32_t mbits = (mq[k >> 2] >> (8 * (k & 3))) & 0xFFu;
-              const uint32_t vbits = (vq[k >> 2] >> (8 * (k & 3))) & 0xFFu;
-              float m = f_mul(e4m3_to_float(static_cast<uint8_t>(mbits)), s_m_t);
-              float v = f_mul(e5m2_to_float(static_cast<uint8_t>(vbits)), s_v_t);
-              w[k] = adamw_update(w[k], __uint_as_float(acc[16 * g + k]), m, v, hy);
-              // rows / columns beyond the matrix hold zeros (zero-filled loads), so they never
-              // raise the running maxima
-              amax_m_t = fmaxf(amax_m_t, fabsf(m));
-              amax_v_t = fmaxf(amax_v_t, fabsf(v));
-              mo[k >> 2] |= static_cast<uint32_t>(e4m3_code(f_mul(m, inv_m_t))) << (8 * (k & 3));
-              vo[k >> 2] |= static_cast<uint32_t>(e5m2_code(f_mul(v, inv_v_t))) << (8 * (k & 3));
+            for (int k = 0; k < 16; k += 2) {
+              float m0, m1, v0, v1;
+              e4m3x2_to_float(mq[k >> 2] >> (8 * (k & 3)), m0, m1);
+              e5m2x2_to_float(vq[k >> 2] >> (8 * (k & 3)), v0, v1);
+              m0 = f_mul(m0, s_m_t);
+              m1 = f_mul(m1, s_m_t);
+              v0 = f_mul(v0, s_v_t);
+              v1 = f_mul(v1, s_v_t);
+              w[k] = adamw_update(w[k], __uint_as_float(acc[16 * g + k]), m0, v0, hy);
+              w[k + 1] = adamw_update(w[k + 1], __uint_as_float(acc[16 * g + k + 1]), m1, v1, hy);
+              // rows / columns beyond the matrix hold zeros (zero-filled loads), so they never raise
+              // the running maxima
+              amax_m_t = fmaxf(amax_m_t, fmaxf(fabsf(m0), fabsf(m1)));
+              amax_v_t = fmaxf(amax_v_t, fmaxf(fabsf(v0), fabsf(v1)));
+              // the conversions saturate to +-448 / +-57344, which is the reference's clamp
+              mo[k >> 2] |= e4m3x2_code_bits(f_mul(m0, inv_m_t), f_mul(m1, inv_m_t)) << (8 * (k & 3));
+              vo[k >> 2] |= e5m2x2_code_bits(f_mul(v0, inv_v_t), f_mul(v1, inv_v_t)) << (8 * (k & 3));
             }
             store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
             st16_bytes(mb, r, g, mo);
