@@ -27,6 +27,7 @@ N > 1      row-sharded tensor parallelism: rank r owns rows [r V/N, (r+1) V/N) o
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -224,7 +225,16 @@ def run_forge(args):
             pin[key] = t.cpu().pin_memory()
         return pin[key]
 
-    def step_device(step_no):
+    hyper_dev = K.DeviceHyper(dev)
+
+    def set_step(step_no):
+        """New bias corrections for this step: 64 bytes packed on the host; the copy to the device
+        block is part of the step (a memcpy node when the step is a captured graph)."""
+        h = K._hyper(step=step_no, **HYPER)
+        _lib.check(_lib.load().forge_hyper_pack(ctypes.byref(h), hyper_dev.host.data_ptr()), "forge_hyper_pack")
+
+    def step_device(step_no=None):
+        hyper_dev.dev.copy_(hyper_dev.host, non_blocking=True)
         last_grp, xg = None, None
         for name, V, H, grp, r0, r1, w, m, v in params:
             if world > 1:
@@ -234,7 +244,7 @@ def run_forge(args):
                 x = xg
             else:
                 x = x_full[H]
-            K.fused_grad_adamw(dys[r1 - r0], x, w, m, v, step=step_no, **HYPER)
+            K.fused_grad_adamw(dys[r1 - r0], x, w, m, v, hyper_device=hyper_dev)
 
     stage = {}
 
@@ -246,8 +256,9 @@ def run_forge(args):
 
     host_result = torch.zeros(2, dtype=torch.float32).pin_memory()
 
-    def step_host(step_no):
+    def step_host(step_no=None, sync=True):
         """Same step, inputs start in pinned host memory; returns H2D / D2H bytes moved."""
+        hyper_dev.dev.copy_(hyper_dev.host, non_blocking=True)
         h2d = 0
         last_grp, xg = None, None
         for name, V, H, grp, r0, r1, w, m, v in params:
@@ -269,11 +280,12 @@ def run_forge(args):
                 x = staged(x_full[H], "x")
                 x.copy_(x_h, non_blocking=True)
                 h2d += x_h.numel() * 2
-            K.fused_grad_adamw(dy_d, x, w, m, v, step=step_no, **HYPER)
+            K.fused_grad_adamw(dy_d, x, w, m, v, hyper_device=hyper_dev)
         # the step's result: the device status word and one updated weight, read back to the host
         host_result[0:1].copy_(_lib.status_word(dev)[0:1].float(), non_blocking=True)
         host_result[1:2].copy_(params[-1][6][0, 0:1].float(), non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        if sync:
+            torch.cuda.current_stream().synchronize()
         return h2d, 8
 
     def barrier():
@@ -281,13 +293,41 @@ def run_forge(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, first_step):
+    def capture(fn):
+        """The step as a CUDA graph: 225 launches (+ gathers / copies) replayed with one call, the
+        per-step hyper-parameters arriving through the device block.  Falls back to eager launches if
+        capture is refused."""
+        if args.eager:
+            return None
+        try:
+            g = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fn()                       # warm-up on the capture stream
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g):
+                fn()
+            return g
+        except Exception as e:  # pragma: no cover - depends on the driver / NCCL
+            sys.stderr.write(f"[bench] graph capture failed ({type(e).__name__}: {e}); eager launches\n")
+            torch.cuda.synchronize()
+            return None
+
+    def timed(fn, steps, first_step, graph=None, after=None):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         extra = None
         for s in range(steps):
-            extra = fn(first_step + s)
+            set_step(first_step + s)
+            if graph is not None:
+                graph.replay()
+            else:
+                extra = fn(first_step + s)
+            if after is not None:
+                after()
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1) / steps
@@ -299,19 +339,29 @@ def run_forge(args):
 
     W = max(args.warmup, 3)
     step_no = 1
+    set_step(step_no)
+    step_device()                        # first launches set function attributes; never captured
+    step_no += 1
+    torch.cuda.synchronize()
+    g_dev = capture(step_device)
     for _ in range(W):
-        step_device(step_no)
+        set_step(step_no)
+        g_dev.replay() if g_dev is not None else step_device()
         step_no += 1
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    ms_dev, _ = timed(step_device, args.steps, step_no)
+    ms_dev, _ = timed(step_device, args.steps, step_no, graph=g_dev)
     step_no += args.steps
 
-    step_host(step_no)
+    # end-to-end arm: host inputs copied in every step, result read back and waited for every step
+    set_step(step_no)
+    moved = step_host()
     step_no += 1
+    g_e2e = capture(lambda: step_host(sync=False))
     e2e_steps = max(1, min(args.steps, 5))
-    ms_e2e, moved = timed(step_host, e2e_steps, step_no)
+    ms_e2e, _ = timed(step_host, e2e_steps, step_no, graph=g_e2e,
+                      after=(lambda: torch.cuda.current_stream().synchronize()) if g_e2e is not None else None)
     step_no += e2e_steps
     clocks = sampler.stop() if sampler else None
     status = _lib.read_status(dev)
@@ -334,7 +384,8 @@ def run_forge(args):
             "steps": args.steps, "warmup": W, "ms_per_step": ms_dev, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "bt": BT, "linears": launches, "weights": "bf16", "moments": "bf16",
-                       "optimizer": "adamw", "parallelism": f"tp{world}-rows" if world > 1 else "single",
+                       "optimizer": "adamw", "launch": "cuda_graph" if g_dev is not None else "eager",
+                       "parallelism": f"tp{world}-rows" if world > 1 else "single",
                        "l2": "each weight and its moments are distinct buffers (45 GB in total), so every launch "
                              "streams state that is not in L2; no flush needed",
                        "parameters": sum(V * H for _, V, H, *_ in params)},
@@ -400,6 +451,7 @@ def main():
     ap.add_argument("--impl", default="forge", choices=["forge", "reference"])
     ap.add_argument("--workload", default="llama3.1-8b-linears")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

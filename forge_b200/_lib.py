@@ -85,6 +85,7 @@ class ForgeWgradArgs(ctypes.Structure):
         ("scratch", ctypes.c_void_p),
         ("scratch_bytes", ctypes.c_size_t),
         ("status", ctypes.c_void_p),
+        ("hyper_device", ctypes.c_void_p),
     ]
 
 
@@ -109,6 +110,7 @@ class ForgeOptimArgs(ctypes.Structure):
 _SIGNATURES = {
     "forge_wgrad_update": (ctypes.c_int, [ctypes.POINTER(ForgeWgradArgs), ctypes.c_void_p]),
     "forge_wgrad_update_static_scratch": (ctypes.c_int, [ctypes.POINTER(ForgeWgradArgs), ctypes.c_void_p]),
+    "forge_hyper_pack": (ctypes.c_int, [ctypes.POINTER(ForgeHyper), ctypes.c_void_p]),
     "forge_wgrad_scratch_bytes": (ctypes.c_size_t, [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32]),
     "forge_optimizer_update": (ctypes.c_int, [ctypes.POINTER(ForgeOptimArgs), ctypes.c_void_p]),
     "forge_fp8_prestep": (ctypes.c_int, [ctypes.c_void_p] * 5),

@@ -171,7 +171,10 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
   if (opt == FORGE_OPT_SGD) st = FORGE_ST_NONE;
   if (opt != FORGE_OPT_SGD && (st < FORGE_ST_F32 || st > FORGE_ST_FP8_TENSOR))
     return fail(FORGE_ERR_INVALID_ARG, "unknown state mode %d", st);
-  if (a.hyper.step < 1 && opt == FORGE_OPT_ADAMW) return fail(FORGE_ERR_INVALID_ARG, "step must be >= 1 (got %d)", a.hyper.step);
+  if (a.hyper_device == nullptr && a.hyper.step < 1 && opt == FORGE_OPT_ADAMW)
+    return fail(FORGE_ERR_INVALID_ARG, "step must be >= 1 (got %d)", a.hyper.step);
+  if (a.hyper_device != nullptr && (reinterpret_cast<uintptr_t>(a.hyper_device) & 15u) != 0)
+    return fail(FORGE_ERR_ALIGNMENT, "hyper_device is not 16-byte aligned");
 
   const DeviceInfo* di = current_device_info();
   if (di == nullptr) return FORGE_ERR_CUDA;
@@ -241,6 +244,7 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
   p.m_absmax = a.state.m_absmax_next;
   p.v_absmax = a.state.v_absmax_next;
   p.status = a.status;
+  p.hyper_dev = static_cast<const Hyper*>(a.hyper_device);
   if (a.w_dtype == FORGE_DT_BF16) return dispatch_wgrad<DT_BF16>(opt, st, tm_dy, tm_x, t, p, di->sm_count, stream);
   return dispatch_wgrad<DT_F32>(opt, st, tm_dy, tm_x, t, p, di->sm_count, stream);
 }
@@ -299,4 +303,15 @@ extern "C" int forge_wgrad_update_static_scratch(const ForgeWgradArgs* args, voi
   a.scratch = scratch;
   a.scratch_bytes = static_cast<size_t>(FORGE_STATIC_SCRATCH_BYTES);
   return forge_wgrad_update(&a, cuda_stream);
+}
+
+static_assert(sizeof(forge::Hyper) <= FORGE_HYPER_DEVICE_BYTES, "packed hyper block too small");
+
+extern "C" int forge_hyper_pack(const ForgeHyper* h, void* out) {
+  if (h == nullptr || out == nullptr) return fail(FORGE_ERR_INVALID_ARG, "forge_hyper_pack: null pointer");
+  if (h->step < 1) return fail(FORGE_ERR_INVALID_ARG, "step must be >= 1 (got %d)", h->step);
+  memset(out, 0, FORGE_HYPER_DEVICE_BYTES);
+  const forge::Hyper packed = forge::make_hyper(*h);
+  memcpy(out, &packed, sizeof(packed));
+  return FORGE_OK;
 }

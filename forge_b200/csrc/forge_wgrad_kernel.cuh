@@ -39,6 +39,9 @@ constexpr int UMMA_K = 16;
 #ifndef FORGE_OP_STAGES
 #define FORGE_OP_STAGES 3
 #endif
+#ifndef FORGE_STATE_LOAD_ROWS
+#define FORGE_STATE_LOAD_ROWS 128
+#endif
 #ifndef FORGE_MAX_STATE_STAGES
 #define FORGE_MAX_STATE_STAGES 6
 #endif
@@ -190,6 +193,7 @@ struct WgradParams {
   float* m_absmax;     // fp8-tensor: next-step absmax accumulators (atomic max)
   float* v_absmax;
   int* status;         // device status word: 0 = ok
+  const Hyper* hyper_dev;  // optional: hyper-parameters read from device memory instead of `hyper`
 };
 
 // bytes one pipeline stage of W + moments takes for a chunk of `cn` columns
@@ -302,9 +306,9 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
   }
   if (warp == 0 && lane == 0) { prefetch_tmap(&tm_dy); prefetch_tmap(&tm_x); }
   if (warp == 2 && lane == 0) {
-    prefetch_tmap(&tl_w);
-    if (NMOM > 0) prefetch_tmap(&tl_m);
-    if (NMOM > 1) prefetch_tmap(&tl_v);
+    prefetch_tmap(FORGE_STATE_LOAD_ROWS == 128 ? &tl_w : &tm_w);
+    if (NMOM > 0) prefetch_tmap(FORGE_STATE_LOAD_ROWS == 128 ? &tl_m : &tm_m);
+    if (NMOM > 1) prefetch_tmap(FORGE_STATE_LOAD_ROWS == 128 ? &tl_v : &tm_v);
   }
   tc_fence_before();
   __syncthreads();
@@ -406,20 +410,34 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           uint8_t* wb = st_buf + s * Cfg::kStageBytes;
           mbar_expect_tx(&ctrl->st_full[s], Cfg::kStageBytes);
           const int cc = col0 + c * CN;
+          // LOAD_ROWS rows per box.  Measured on a 14336 x 4096 bf16 update at BT = 512: 128-row boxes
+          // with CTA pairs 152 us, 32-row boxes with CTA pairs 160 us, 32-row boxes with single CTAs
+          // 156 us, 128-row boxes with single CTAs 169 us.
+          constexpr int LOAD_ROWS = FORGE_STATE_LOAD_ROWS;
 #pragma unroll
-          for (int bx = 0; bx < BoxGeom<WRB>::kBoxes; ++bx)
-            tma_load_2d(wb + bx * BoxGeom<WRB>::kBoxBytes, &tl_w, &ctrl->st_full[s], cc + bx * WBC, row0, pol);
-          if constexpr (NMOM > 0) {
-            uint8_t* mb = wb + Cfg::kWBytes;
+          for (int rb = 0; rb < 128 / LOAD_ROWS; ++rb) {
+            const int rr = row0 + LOAD_ROWS * rb;
+            const CUtensorMap* lw = (LOAD_ROWS == 128) ? &tl_w : &tm_w;
+            const CUtensorMap* lm = (LOAD_ROWS == 128) ? &tl_m : &tm_m;
+            const CUtensorMap* lv = (LOAD_ROWS == 128) ? &tl_v : &tm_v;
 #pragma unroll
-            for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-              tma_load_2d(mb + bx * BoxGeom<SRB>::kBoxBytes, &tl_m, &ctrl->st_full[s], cc + bx * SBC, row0, pol);
-          }
-          if constexpr (NMOM > 1) {
-            uint8_t* vb = wb + Cfg::kWBytes + Cfg::kSBytes;
+            for (int bx = 0; bx < BoxGeom<WRB>::kBoxes; ++bx)
+              tma_load_2d(wb + bx * BoxGeom<WRB>::kBoxBytes + rb * LOAD_ROWS * BoxGeom<WRB>::kPitch, lw,
+                          &ctrl->st_full[s], cc + bx * WBC, rr, pol);
+            if constexpr (NMOM > 0) {
+              uint8_t* mb = wb + Cfg::kWBytes;
 #pragma unroll
-            for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-              tma_load_2d(vb + bx * BoxGeom<SRB>::kBoxBytes, &tl_v, &ctrl->st_full[s], cc + bx * SBC, row0, pol);
+              for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
+                tma_load_2d(mb + bx * BoxGeom<SRB>::kBoxBytes + rb * LOAD_ROWS * BoxGeom<SRB>::kPitch, lm,
+                            &ctrl->st_full[s], cc + bx * SBC, rr, pol);
+            }
+            if constexpr (NMOM > 1) {
+              uint8_t* vb = wb + Cfg::kWBytes + Cfg::kSBytes;
+#pragma unroll
+              for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
+                tma_load_2d(vb + bx * BoxGeom<SRB>::kBoxBytes + rb * LOAD_ROWS * BoxGeom<SRB>::kPitch, lv,
+                            &ctrl->st_full[s], cc + bx * SBC, rr, pol);
+            }
           }
         }
       }
@@ -429,7 +447,7 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
     const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
     const int wg = (warp - EPI_WARP0) >> 2;       // 0 or 1
     const int r = quarter * 32 + lane;            // row inside the tile
-    const Hyper hy = p.hyper;
+    const Hyper hy = (p.hyper_dev != nullptr) ? *p.hyper_dev : p.hyper;
     // stores: normal priority, so that the partial lines of neighbouring chunks merge in L2
     const uint64_t pol = policy_evict_normal();
     float s_m_t = 1.0f, s_v_t = 1.0f, inv_m_t = 1.0f, inv_v_t = 1.0f;

@@ -80,7 +80,29 @@ _wgrad_cache: dict[tuple, ForgeWgradArgs] = {}
 _WGRAD_CACHE_MAX = 4096
 
 
-def _wgrad(grad_output, input, weight, optimizer, state, hyper):
+class DeviceHyper:
+    """Hyper-parameters kept in device memory so that captured CUDA graphs can be replayed with a
+    new lr / step: ``update(...)`` packs them on the host (same narrowing as the direct path) and
+    enqueues one 64-byte copy on the current stream; pass the object as ``hyper_device=`` to the
+    fused operators."""
+
+    NBYTES = 64
+
+    def __init__(self, device):
+        self.host = torch.zeros(self.NBYTES, dtype=torch.uint8).pin_memory()
+        self.dev = torch.zeros(self.NBYTES, dtype=torch.uint8, device=device)
+
+    def update(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1, momentum=0.0, nesterov=False):
+        h = _hyper(lr, beta1, beta2, eps, weight_decay, step, momentum, nesterov)
+        _lib.check(_lib.load().forge_hyper_pack(ctypes.byref(h), self.host.data_ptr()), "forge_hyper_pack")
+        self.dev.copy_(self.host, non_blocking=True)
+        return self
+
+    def data_ptr(self):
+        return self.dev.data_ptr()
+
+
+def _wgrad(grad_output, input, weight, optimizer, state, hyper, hyper_device=None):
     if not (grad_output.is_cuda and input.is_cuda and weight.is_cuda):
         _require_cuda(grad_output, input, weight)
     assert grad_output.is_contiguous() and input.is_contiguous()
@@ -116,6 +138,7 @@ def _wgrad(grad_output, input, weight, optimizer, state, hyper):
     a.dY, a.X, a.BT = grad_output.data_ptr(), input.data_ptr(), BT
     a.state = state
     a.hyper = hyper
+    a.hyper_device = hyper_device.data_ptr() if hyper_device is not None else None
     scratch = None
     if odt != torch.bfloat16:
         nbytes = lib.forge_wgrad_scratch_bytes(BT, V, H, a.operand_dtype)
@@ -174,11 +197,14 @@ def fused_grad_sgd(grad_output, input, weight, lr: float = 1e-3, weight_decay: f
 
 
 def fused_grad_adamw(grad_output, input, weight, m, v, lr: float = 1e-4, beta1: float = 0.9,
-                     beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.01, step: int = 1):
-    """Fused weight gradient + AdamW update (``kernel.py:1342-1455``); m, v bf16 or fp32, in place."""
+                     beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.01, step: int = 1,
+                     hyper_device: "DeviceHyper | None" = None):
+    """Fused weight gradient + AdamW update (``kernel.py:1342-1455``); m, v bf16 or fp32, in place.
+    ``hyper_device`` (no reference counterpart): read the hyper-parameters from a ``DeviceHyper`` block
+    at run time instead of the keyword values, for replay inside a captured CUDA graph."""
     _require_cuda(m, v)
     _wgrad(grad_output, input, weight, OPT_ADAMW, _moment_state(m, v),
-           _hyper(lr, beta1, beta2, eps, weight_decay, step))
+           _hyper(lr, beta1, beta2, eps, weight_decay, step), hyper_device)
 
 
 def optimizer_only_adamw(grad, weight, m, v, lr: float = 1e-4, beta1: float = 0.9, beta2: float = 0.999,

@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define FORGE_ABI_VERSION 1
+#define FORGE_ABI_VERSION 2
 
 /* error codes */
 #define FORGE_OK 0
@@ -98,7 +98,22 @@ typedef struct ForgeWgradArgs {
   size_t scratch_bytes;
   int32_t* status;           /* optional device word; a kernel that abandons a wait writes its
                                 code here (0 = ok); see forge_read_status                       */
+  const void* hyper_device;  /* optional: FORGE_HYPER_DEVICE_BYTES of DEVICE memory holding the output
+                                of forge_hyper_pack.  When non-NULL the kernel reads its
+                                hyper-parameters from there at run time and `hyper` is ignored, so
+                                a captured CUDA graph can be replayed with a new lr / step by
+                                rewriting that block before each replay.                         */
 } ForgeWgradArgs;
+
+/* Bytes of the packed hyper-parameter block. */
+#define FORGE_HYPER_DEVICE_BYTES 64
+
+/* Narrows `h` exactly as forge_wgrad_update does internally (bias corrections in double, then
+ * float) and writes the FORGE_HYPER_DEVICE_BYTES block the kernels read into HOST memory `out`;
+ * copy it to the device buffer passed as ForgeWgradArgs.hyper_device.  No reference counterpart
+ * (the reference passes hyper-parameters as kernel arguments, src/fused_grad_optimizer/
+ * kernel.py:1367-1368, which pins them into a captured graph). */
+int forge_hyper_pack(const ForgeHyper* h, void* out);
 
 /* Fused dW = dY^T X and in-place optimizer update of W and its moments; no gradient tensor is
  * written to memory.  Replaces the reference's fused_grad_adamw / fused_grad_sgd /

@@ -384,3 +384,33 @@ def test_error_conventions():
                          torch.zeros(100, 92, dtype=torch.bfloat16, device=DEV))
     with pytest.raises(_lib.ForgeLibraryError):  # CPU tensors: no fallback
         K.fused_grad_sgd(dy.cpu(), x.cpu(), w.cpu())
+
+
+def test_device_hyper_and_graph_replay():
+    """Hyper-parameters read from device memory: same bits as the direct path, and a captured CUDA
+    graph replays correctly with a new lr / step after the device block is rewritten."""
+    BT, V, H = 192, 384, 512
+    dy, x, w, m, v = gen_inputs(31, BT, V, H)
+    dyd, xd = dy.bfloat16().to(DEV), x.bfloat16().to(DEV)
+    ref = [t.bfloat16().to(DEV) for t in (w, m, v)]
+    got = [t.bfloat16().to(DEV) for t in (w, m, v)]
+    hd = K.DeviceHyper(torch.device(DEV, torch.cuda.current_device()))
+    # warm-up outside capture (first launch sets function attributes)
+    scratch = [t.clone() for t in got]
+    hd.update(lr=1e-3, step=1, weight_decay=0.01)
+    K.fused_grad_adamw(dyd, xd, *scratch, hyper_device=hd)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        hd.dev.copy_(hd.host, non_blocking=True)
+        K.fused_grad_adamw(dyd, xd, *got, hyper_device=hd)
+    for step, lr in ((1, 1e-3), (2, 5e-4), (3, 2e-3)):
+        K.fused_grad_adamw(dyd, xd, *ref, lr=lr, weight_decay=0.01, step=step)
+        h = K._hyper(lr, weight_decay=0.01, step=step)
+        from forge_b200 import _lib
+        import ctypes
+        _lib.check(_lib.load().forge_hyper_pack(ctypes.byref(h), hd.host.data_ptr()), "pack")
+        graph.replay()
+        torch.cuda.synchronize()
+        for a, b in zip(ref, got):
+            assert torch.equal(a.view(torch.int16), b.view(torch.int16)), f"step {step}"
