@@ -17,8 +17,11 @@ training where the preceding kernel has just produced them.
            its X and dY from pinned host memory, and each step ends with a device-to-host read of a
            status word and one updated weight.
 N > 1      row-sharded tensor parallelism: rank r owns rows [r V/N, (r+1) V/N) of every weight and
-           moment; X arrives feature-sharded and is all-gathered by NCCL once per group of linears
-           that share it (q/k/v, gate/up, o, down, lm_head) inside the timed step; strong scaling.
+           moment and updates them from its dY slice and the full X.  The path itself has no exchange
+           step: the forward pass has already all-gathered X (it needs it for Y = X W^T) and autograd
+           saved the gathered tensor, so the backward's fused update is purely local; strong scaling.
+           ``--gather-x`` re-gathers X by NCCL inside the timed step (once per group of linears that
+           share it) for a design that saves the activation shards instead.
 ``--impl reference``  the reference's own CPU-runnable path for this update -- torch autograd +
            ``torch.optim.AdamW`` on the host cores -- on a bounded sample (one decoder layer's seven
            projections), scaled to the full workload by parameter count.
@@ -194,11 +197,12 @@ def run_forge(args):
 
     linears = workload_linears(args.workload)
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    shard_world = args.shard_of if (world == 1 and args.shard_of > 1) else world   # see --shard-of
 
     # state: this rank's rows of every weight and moment
     params = []
     for name, V, H, grp in linears:
-        r0, r1 = row_range(V, rank, world)
+        r0, r1 = row_range(V, rank, shard_world)
         w = torch.empty(r1 - r0, H, dtype=torch.bfloat16, device=dev).normal_(0.0, 0.02, generator=gen)
         m = torch.zeros_like(w)
         v = torch.zeros_like(w)
@@ -233,18 +237,49 @@ def run_forge(args):
         h = K._hyper(step=step_no, **HYPER)
         _lib.check(_lib.load().forge_hyper_pack(ctypes.byref(h), hyper_dev.host.data_ptr()), "forge_hyper_pack")
 
+    # The 225 updates of a step are independent of each other (each touches its own W, m, v), so they
+    # are spread round-robin over a few streams: a kernel that does not fill the GPU (the last wave of
+    # a large projection, the small k / v projections, every shard in the row-sharded mode) overlaps
+    # with its neighbours.  Under graph capture the streams become parallel branches of the graph.
+    n_streams = max(1, args.streams)
+    side_streams = [torch.cuda.Stream() for _ in range(n_streams - 1)]
+    do_gather = world > 1 and args.gather_x
+    comm_stream = torch.cuda.Stream() if do_gather else None
+
     def step_device(step_no=None):
+        main = torch.cuda.current_stream()
         hyper_dev.dev.copy_(hyper_dev.host, non_blocking=True)
-        last_grp, xg = None, None
-        for name, V, H, grp, r0, r1, w, m, v in params:
-            if world > 1:
+        start = torch.cuda.Event()
+        start.record(main)
+        lanes = [main] + side_streams
+        for st in side_streams:
+            st.wait_event(start)
+        # row-sharded mode: the gathers run on their own stream, ahead of the updates that use them
+        gathered = {}
+        if do_gather:
+            comm_stream.wait_event(start)
+            last_grp = None
+            for name, V, H, grp, *_ in params:
                 if grp != last_grp:
-                    xg = all_gather_features(x_shard[H])     # NCCL, lands in local memory
+                    with torch.cuda.stream(comm_stream):
+                        xg = all_gather_features(x_shard[H])     # NCCL, lands in local memory
+                        ev = torch.cuda.Event()
+                        ev.record(comm_stream)
+                    gathered[grp] = (xg, ev)
                     last_grp = grp
-                x = xg
+        for i, (name, V, H, grp, r0, r1, w, m, v) in enumerate(params):
+            st = lanes[i % n_streams]
+            if do_gather:
+                x, ev = gathered[grp]
+                st.wait_event(ev)
             else:
                 x = x_full[H]
-            K.fused_grad_adamw(dys[r1 - r0], x, w, m, v, hyper_device=hyper_dev)
+            with torch.cuda.stream(st):
+                K.fused_grad_adamw(dys[r1 - r0], x, w, m, v, hyper_device=hyper_dev)
+        for st in side_streams + ([comm_stream] if do_gather else []):
+            done = torch.cuda.Event()
+            done.record(st)
+            main.wait_event(done)
 
     stage = {}
 
@@ -266,7 +301,7 @@ def run_forge(args):
             dy_d = staged(dys[r1 - r0], "dy")
             dy_d.copy_(dy_h, non_blocking=True)
             h2d += dy_h.numel() * 2
-            if world > 1:
+            if do_gather:
                 if grp != last_grp:
                     xs_h = pinned(x_shard[H])
                     xs_d = staged(x_shard[H], "x")
@@ -384,8 +419,8 @@ def run_forge(args):
             "steps": args.steps, "warmup": W, "ms_per_step": ms_dev, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "bt": BT, "linears": launches, "weights": "bf16", "moments": "bf16",
-                       "optimizer": "adamw", "launch": "cuda_graph" if g_dev is not None else "eager",
-                       "parallelism": f"tp{world}-rows" if world > 1 else "single",
+                       "optimizer": "adamw", "launch": "cuda_graph" if g_dev is not None else "eager", "streams": n_streams,
+                       "parallelism": (f"tp{world}-rows" + ("+gather-x" if do_gather else "")) if world > 1 else "single",
                        "l2": "each weight and its moments are distinct buffers (45 GB in total), so every launch "
                              "streams state that is not in L2; no flush needed",
                        "parameters": sum(V * H for _, V, H, *_ in params)},
@@ -405,7 +440,14 @@ def run_forge(args):
             line["cpu_baseline"] = cpu_baseline(args.workload)
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # replayed graphs hold NCCL work: drop them and drain the device before tearing NCCL down, and do
+        # not let a stuck finaliser keep the job alive after the result line is out
+        sys.stdout.flush()
+        del g_dev, g_e2e
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 # dram bytes (read + write) inside the launches per algorithmic byte, from the ncu capture summarised
@@ -451,6 +493,12 @@ def main():
     ap.add_argument("--impl", default="forge", choices=["forge", "reference"])
     ap.add_argument("--workload", default="llama3.1-8b-linears")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--streams", type=int, default=4, help="streams the independent updates of a step are spread over")
+    ap.add_argument("--gather-x", action="store_true",
+                    help="N > 1: all-gather the feature-sharded X by NCCL inside the timed step")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="single-GPU diagnostic: give this GPU the row shard rank 0 would own in a job of this "
+                         "many ranks (no communication), to time the kernels at shard sizes")
     ap.add_argument("--eager", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -1,0 +1,96 @@
+"""Row-sharded tensor parallelism on real GPUs (needs two; skipped otherwise): two NCCL ranks train a
+sharded linear for three steps and must reproduce, row for row and bit for bit, the weight a single
+GPU produces; the reduce-scattered input gradient must match the unsharded one."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, mode, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=60))
+    try:
+        from forge_b200 import FusedLinear
+        from forge_b200.tensor_parallel import RowShardedFusedLinear, feature_range
+        g = torch.Generator().manual_seed(5)
+        BT, H, V = 96, 512, 776            # 776 rows -> shards of 392 and 384 rows
+        w0 = (torch.randn(V, H, generator=g) * 0.05).bfloat16()
+        xs = [torch.randn(BT, H, generator=g).bfloat16() for _ in range(3)]
+        gys = [(torch.randn(BT, V, generator=g) * 1e-2).bfloat16() for _ in range(3)]
+        tp = RowShardedFusedLinear.from_full_weight(w0.to(dev), optimizer_type="adamw", state_mode=mode)
+        tp.train()
+        c0, c1 = feature_range(H, rank, world)
+        full = None
+        if rank == 0:
+            full = FusedLinear(H, V, optimizer_type="adamw", state_mode=mode)
+            full.weight.data = w0.clone()
+            full = full.to(dev).to(torch.bfloat16).train()
+        for x, gy in zip(xs, gys):
+            tp.local.update_optimizer_config(lr=1e-2, weight_decay=0.01)
+            xin = x[:, c0:c1].to(dev).requires_grad_(True)
+            y = tp(xin)
+            y.backward(gy[:, tp.row_start:tp.row_end].to(dev))
+            if rank == 0:
+                w_before = full.weight.detach().clone()
+                full.update_optimizer_config(lr=1e-2, weight_decay=0.01)
+                xf = x.to(dev).requires_grad_(True)
+                full(xf).backward(gy.to(dev))
+                ref_dx = (gy.to(dev).double() @ w_before.double())[:, c0:c1]
+                err = (xin.grad.double() - ref_dx).abs().max().item()
+                # each rank's partial dX is rounded to bf16 before NCCL sums it in bf16
+                assert err < 1.5e-2 * ref_dx.abs().max().item() + 1e-6, f"dX shard off by {err}"
+        gathered = tp.gather_full_weight()
+        if rank == 0:
+            assert torch.equal(gathered.view(torch.int16), full.weight.detach().view(torch.int16)), \
+                f"{(gathered != full.weight.detach()).sum().item()} weights differ from the single-GPU run"
+        torch.cuda.synchronize()
+        dist.barrier()
+        q.put((rank, "ok"))
+        dist.destroy_process_group()
+    except Exception as e:  # pragma: no cover
+        q.put((rank, f"{type(e).__name__}: {e}"))
+        os._exit(1)      # do not wait for a peer that is blocked in a collective
+
+
+@pytest.mark.parametrize("mode", ["bf16", "int8", "fp8_block"])
+def test_two_rank_nccl_matches_single_gpu(mode):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = []
+    try:
+        for _ in procs:
+            out.append(q.get(timeout=150))
+            if out[-1][1] != "ok":
+                break
+    except Exception:
+        out.append(("parent", "timed out waiting for the ranks"))
+    for p in procs:
+        p.join(timeout=20)
+        if p.is_alive():
+            p.terminate()
+    assert sorted(out) == [(0, "ok"), (1, "ok")], out
