@@ -1,0 +1,125 @@
+"""Whole-model training step with every ``nn.Linear`` fused (BASELINE configurations 2-4).
+
+Builds a Llama-3.1-8B (or Qwen3-32B) architecture from its config with random weights -- no
+checkpoint, no dataset: tokens are uniform over the vocabulary -- swaps every ``nn.Linear`` for
+``FusedLinear.from_linear`` (same recipe as the reference's README), leaves embeddings and norms to a
+regular ``torch.optim.AdamW``, and reports the median step time and the peak device memory.
+
+    python examples/llama_step.py --model llama3.1-8b --state bf16 --steps 20
+    python examples/llama_step.py --model llama3.1-8b --baseline      # vanilla fused torch AdamW
+
+One JSON line on stdout.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+
+def build_config(name, layers=None):
+    if name == "llama3.1-8b":
+        from transformers import LlamaConfig
+        cfg = LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                          num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5,
+                          rope_theta=500000.0, max_position_embeddings=8192, tie_word_embeddings=False,
+                          attention_bias=False, mlp_bias=False)
+    elif name == "qwen3-32b":
+        from transformers import Qwen3Config
+        cfg = Qwen3Config(vocab_size=151936, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64,
+                          num_attention_heads=64, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
+                          rope_theta=1000000.0, max_position_embeddings=40960, tie_word_embeddings=False,
+                          attention_bias=False)
+    else:
+        raise SystemExit(f"unknown model {name}")
+    if layers:
+        cfg.num_hidden_layers = layers
+    return cfg
+
+
+def swap_linears(module, state_mode, use_dgrad):
+    from forge_b200 import FusedLinear
+    n = 0
+    for name, child in list(module.named_children()):
+        if isinstance(child, torch.nn.Linear):
+            setattr(module, name, FusedLinear.from_linear(child, optimizer_type="adamw", state_mode=state_mode))
+            n += 1
+        else:
+            n += swap_linears(child, state_mode, use_dgrad)
+    return n
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="llama3.1-8b")
+    ap.add_argument("--state", default="bf16", choices=["bf16", "int8", "fp8", "fp8_block"])
+    ap.add_argument("--baseline", action="store_true", help="plain nn.Linear + torch.optim.AdamW(fused=True)")
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--seq", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=0, help="truncate the model (debugging)")
+    ap.add_argument("--forge-dgrad", action="store_true", help="dX through the library's GEMM instead of cuBLAS")
+    args = ap.parse_args()
+
+    from transformers import AutoModelForCausalLM
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = build_config(args.model, args.layers)
+    cfg._attn_implementation = "sdpa"
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = AutoModelForCausalLM.from_config(cfg, dtype=torch.bfloat16)
+    model.train()
+    model.config.use_cache = False
+    n_params = sum(p.numel() for p in model.parameters())
+
+    if args.baseline:
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01, fused=True)
+        manager, fused = None, 0
+    else:
+        from forge_b200 import FusedOptimizerManager, autograd
+        autograd.use_forge_dgrad = args.forge_dgrad
+        fused = swap_linears(model, args.state, args.forge_dgrad)
+        manager = FusedOptimizerManager(model)
+        opt = torch.optim.AdamW(manager.get_non_fused_params(), lr=1e-4, weight_decay=0.01, fused=True)
+
+    torch.cuda.reset_peak_memory_stats(dev)
+    times, losses = [], []
+    for step in range(args.warmup + args.steps):
+        g = torch.Generator(device=dev).manual_seed(1000 + step)
+        ids = torch.randint(0, cfg.vocab_size, (1, args.seq), device=dev, generator=g)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        if manager is not None:
+            manager.pre_step(lr=1e-4, weight_decay=0.01)
+        loss = model(input_ids=ids, labels=ids).loss
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        torch.cuda.synchronize()
+        if step >= args.warmup:
+            times.append((time.perf_counter() - t0) * 1e3)
+        losses.append(loss.item())
+    status = 0
+    if manager is not None:
+        from forge_b200 import _lib
+        status = _lib.read_status(dev)
+    print(json.dumps({
+        "model": args.model, "layers": cfg.num_hidden_layers, "parameters": n_params, "seq": args.seq, "batch": 1,
+        "impl": "torch AdamW(fused=True) baseline" if args.baseline else f"forge_b200 fused linears ({args.state} moments)",
+        "fused_linears": fused, "median_ms_per_step": statistics.median(times), "min_ms": min(times), "max_ms": max(times),
+        "steps": args.steps, "peak_hbm_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
+        "first_loss": losses[0], "last_loss": losses[-1], "device_status": status,
+        "forge_dgrad": bool(args.forge_dgrad), "data": "synthetic uniform tokens, random init",
+    }))
+
+
+if __name__ == "__main__":
+    main()
