@@ -1,0 +1,132 @@
+"""Side-by-side timing of the fused wgrad+AdamW kernel against the reference's own GPU kernels on the
+same B200, per Llama-3.1-8B projection shape at BT = 512 (bf16 W, bf16 moments).
+
+    python baseline/compare_kernels.py            # single GPU only
+
+Arms (each skipped with a note if it cannot be loaded):
+  forge        forge_b200.kernel.fused_grad_adamw (this repository)
+  ref-triton   the reference's default kernel, ``fused_grad_optimizer.kernel.fused_grad_adamw``
+               (persistent Triton kernel for >= 256 tiles, autotuned one below)
+  ref-b200     the reference's B200 Triton kernel, ``kernel_b200_ws.fused_grad_adamw_b200_ws``
+  ref-evt      the reference's CUTLASS Sm100 EVT kernel with its picker's default tile per shape
+               (needs ``baseline/build_reference_evt.py`` to have been run)
+  unfused      dW = dY^T X by cuBLAS, then ``torch._fused_adamw_`` (torch.optim.AdamW(fused=True))
+
+The reference is imported from ``baseline/_ref`` (``pip install --target baseline/_ref <reference>``),
+which must come first on ``sys.path`` because this repository ships an alias package of the same
+import name.  Timing: CUDA events, median of 30, a 256 MB buffer written between iterations to flush L2.
+One JSON object per shape on stdout.
+"""
+
+import json
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+sys.path.insert(0, os.path.join(HERE, "_ref"))          # the reference's fused_grad_optimizer
+sys.path.append(ROOT)                                   # forge_b200 (and, later in the path, the alias)
+
+import torch  # noqa: E402
+
+BT = 512
+SHAPES = [("q/o", 4096, 4096), ("k/v", 1024, 4096), ("gate/up", 14336, 4096), ("down", 4096, 14336)]
+HYPER = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01)
+HBM = 6460.2e9
+
+
+def timeit(fn, flush, iters=30):
+    for s in range(1, 4):
+        fn(s)
+    torch.cuda.synchronize()
+    ts = []
+    for it in range(iters):
+        flush.fill_(it & 0xFF)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn(4 + it)
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def load_arms():
+    arms, notes = {}, {}
+    from forge_b200 import kernel as FK
+    arms["forge"] = FK.fused_grad_adamw
+    try:
+        import fused_grad_optimizer.kernel as RK
+        assert "_ref" in RK.__file__, RK.__file__
+        arms["ref-triton"] = RK.fused_grad_adamw
+    except Exception as e:  # pragma: no cover
+        notes["ref-triton"] = f"{type(e).__name__}: {e}"
+    try:
+        from fused_grad_optimizer.kernel_b200_ws import fused_grad_adamw_b200_ws
+        arms["ref-b200"] = fused_grad_adamw_b200_ws
+    except Exception as e:  # pragma: no cover
+        notes["ref-b200"] = f"{type(e).__name__}: {e}"
+    try:
+        sys.path.insert(0, os.path.join(HERE, "_ref", "evt", "build"))
+        import ref_evt_sm100 as EVT
+        from fused_grad_optimizer.cutlass_evt_b200 import _BT_HINT, _pick_tile
+
+        def evt(go, inp, w, m, v, lr, beta1, beta2, eps, weight_decay, step):
+            _BT_HINT["BT"] = go.shape[0]
+            tile = _pick_tile(go.shape[1], inp.shape[1])
+            fn = getattr(EVT, "blackwell_evt_adamw_" + tile)
+            fn(go, inp, w, m, v, lr, beta1, beta2, eps, weight_decay, 1.0 - beta1 ** step, 1.0 - beta2 ** step)
+        arms["ref-evt"] = evt
+    except Exception as e:  # pragma: no cover
+        notes["ref-evt"] = f"{type(e).__name__}: {e}"
+
+    def unfused(go, inp, w, m, v, lr, beta1, beta2, eps, weight_decay, step):
+        g = go.t() @ inp
+        torch._fused_adamw_([w], [g], [m], [v], [], [unfused.step_t], amsgrad=False, lr=lr, beta1=beta1, beta2=beta2,
+                            weight_decay=weight_decay, eps=eps, maximize=False)
+    unfused.step_t = torch.tensor(3.0, device="cuda")
+    arms["unfused"] = unfused
+    return arms, notes
+
+
+def main():
+    dev = "cuda"
+    arms, notes = load_arms()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for name, V, H in SHAPES:
+        g = torch.Generator(device=dev).manual_seed(0)
+        dy = (torch.randn(BT, V, device=dev, generator=g) * 1e-2).bfloat16()
+        x = torch.randn(BT, H, device=dev, generator=g).bfloat16()
+        row = {"shape": name, "V": V, "H": H, "BT": BT}
+        bytes_ = 12 * V * H + 2 * BT * (V + H)
+        row["roofline_us"] = bytes_ / HBM * 1e6
+        ref_w = None
+        for arm, fn in arms.items():
+            w = (torch.randn(V, H, device=dev, generator=torch.Generator(device=dev).manual_seed(1)) * 0.02).bfloat16()
+            m, v = torch.zeros_like(w), torch.zeros_like(w)
+            try:
+                us = timeit(lambda s: fn(dy, x, w, m, v, step=s, **HYPER), flush)
+                row[arm + "_us"] = round(us, 1)
+                row[arm + "_frac"] = round(row["roofline_us"] / us, 3)
+            except Exception as e:  # pragma: no cover
+                row[arm + "_error"] = f"{type(e).__name__}: {str(e)[:160]}"
+                torch.cuda.synchronize()
+                continue
+            # agreement after one step from identical state
+            w1 = (torch.randn(V, H, device=dev, generator=torch.Generator(device=dev).manual_seed(1)) * 0.02).bfloat16()
+            m1, v1 = torch.zeros_like(w1), torch.zeros_like(w1)
+            fn(dy, x, w1, m1, v1, step=1, **HYPER)
+            torch.cuda.synchronize()
+            if arm == "forge":
+                ref_w = (w1.float(), m1.float(), v1.float())
+            elif ref_w is not None and arm != "unfused":
+                row[arm + "_max_abs_dW_vs_forge"] = float((w1.float() - ref_w[0]).abs().max())
+                row[arm + "_max_rel_dm_vs_forge"] = float(((m1.float() - ref_w[1]).abs() / (ref_w[1].abs() + 1e-6)).max())
+        for k, vnote in notes.items():
+            row[k + "_unavailable"] = vnote
+        print(json.dumps(row), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -232,10 +232,9 @@ def run_forge(args):
     hyper_dev = K.DeviceHyper(dev)
 
     def set_step(step_no):
-        """New bias corrections for this step: 64 bytes packed on the host; the copy to the device
-        block is part of the step (a memcpy node when the step is a captured graph)."""
-        h = K._hyper(step=step_no, **HYPER)
-        _lib.check(_lib.load().forge_hyper_pack(ctypes.byref(h), hyper_dev.host.data_ptr()), "forge_hyper_pack")
+        """New bias corrections for this step: 64 bytes packed on the host and copied to the device
+        block the kernels read (enqueued on the stream ahead of the step, captured or not)."""
+        hyper_dev.update(step=step_no, **HYPER)
 
     # The 225 updates of a step are independent of each other (each touches its own W, m, v), so they
     # are spread round-robin over a few streams: a kernel that does not fill the GPU (the last wave of
@@ -248,7 +247,6 @@ def run_forge(args):
 
     def step_device(step_no=None):
         main = torch.cuda.current_stream()
-        hyper_dev.dev.copy_(hyper_dev.host, non_blocking=True)
         start = torch.cuda.Event()
         start.record(main)
         lanes = [main] + side_streams
@@ -293,7 +291,6 @@ def run_forge(args):
 
     def step_host(step_no=None, sync=True):
         """Same step, inputs start in pinned host memory; returns H2D / D2H bytes moved."""
-        hyper_dev.dev.copy_(hyper_dev.host, non_blocking=True)
         h2d = 0
         last_grp, xg = None, None
         for name, V, H, grp, r0, r1, w, m, v in params:

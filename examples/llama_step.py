@@ -66,6 +66,9 @@ def main():
     ap.add_argument("--seq", type=int, default=512)
     ap.add_argument("--layers", type=int, default=0, help="truncate the model (debugging)")
     ap.add_argument("--forge-dgrad", action="store_true", help="dX through the library's GEMM instead of cuBLAS")
+    ap.add_argument("--graph", action="store_true",
+                    help="capture forward + backward (with the fused updates) + the small optimizer into one CUDA "
+                         "graph and replay it; hyper-parameters reach the fused kernels through device memory")
     args = ap.parse_args()
 
     from transformers import AutoModelForCausalLM
@@ -88,21 +91,55 @@ def main():
         autograd.use_forge_dgrad = args.forge_dgrad
         fused = swap_linears(model, args.state, args.forge_dgrad)
         manager = FusedOptimizerManager(model)
-        opt = torch.optim.AdamW(manager.get_non_fused_params(), lr=1e-4, weight_decay=0.01, fused=True)
+        if args.graph:
+            manager.enable_device_hyper(dev)
+        opt = torch.optim.AdamW(manager.get_non_fused_params(), lr=1e-4, weight_decay=0.01, fused=True,
+                                capturable=args.graph)
 
     torch.cuda.reset_peak_memory_stats(dev)
     times, losses = [], []
-    for step in range(args.warmup + args.steps):
-        g = torch.Generator(device=dev).manual_seed(1000 + step)
-        ids = torch.randint(0, cfg.vocab_size, (1, args.seq), device=dev, generator=g)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        if manager is not None:
-            manager.pre_step(lr=1e-4, weight_decay=0.01)
+    static_ids = torch.zeros(1, args.seq, dtype=torch.long, device=dev)
+    static_loss = torch.zeros((), device=dev)
+
+    def one_step(ids):
         loss = model(input_ids=ids, labels=ids).loss
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)
+        return loss
+
+    graph = None
+    # whole-network capture: the eager warm-up must not run on the legacy default stream, or autograd
+    # later ties the captured backward to it
+    side = torch.cuda.Stream() if args.graph else None
+    if side is not None:
+        side.wait_stream(torch.cuda.current_stream())
+        torch.cuda.set_stream(side)
+    for step in range(args.warmup + args.steps):
+        g = torch.Generator(device=dev).manual_seed(1000 + step)
+        ids = torch.randint(0, cfg.vocab_size, (1, args.seq), device=dev, generator=g)
+        if args.graph and graph is None and step == 2:
+            # two eager steps have allocated every state buffer; capture the third
+            static_ids.copy_(ids)
+            if manager is not None:
+                manager.pre_step(lr=1e-4, weight_decay=0.01)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_loss.copy_(one_step(static_ids).detach())
+            graph.replay()
+            torch.cuda.synchronize()
+            losses.append(static_loss.item())
+            continue
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        if manager is not None:
+            manager.pre_step(lr=1e-4, weight_decay=0.01)
+        if graph is not None:
+            static_ids.copy_(ids)
+            graph.replay()
+            loss = static_loss
+        else:
+            loss = one_step(ids)
         torch.cuda.synchronize()
         if step >= args.warmup:
             times.append((time.perf_counter() - t0) * 1e3)
@@ -117,7 +154,7 @@ def main():
         "fused_linears": fused, "median_ms_per_step": statistics.median(times), "min_ms": min(times), "max_ms": max(times),
         "steps": args.steps, "peak_hbm_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
         "first_loss": losses[0], "last_loss": losses[-1], "device_status": status,
-        "forge_dgrad": bool(args.forge_dgrad), "data": "synthetic uniform tokens, random init",
+        "forge_dgrad": bool(args.forge_dgrad), "cuda_graph": bool(args.graph), "data": "synthetic uniform tokens, random init",
     }))
 
 

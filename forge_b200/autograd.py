@@ -96,17 +96,18 @@ def _apply_fused(grad_output_2d, input_2d, weight, state, config, l2_manager=Non
     inp = input_2d if input_2d.is_contiguous() else input_2d.contiguous()
     w = weight.data
     opt = config.optimizer_type
+    hd = getattr(config, "hyper_device", None)
     if opt == "sgd":
-        K.fused_grad_sgd(go, inp, w, lr=config.lr, weight_decay=config.weight_decay)
+        K.fused_grad_sgd(go, inp, w, lr=config.lr, weight_decay=config.weight_decay, hyper_device=hd)
     elif opt == "sgdm":
         K.fused_grad_sgd_momentum(go, inp, w, state.m, lr=config.lr, momentum=config.momentum,
-                                  weight_decay=config.weight_decay, nesterov=config.nesterov)
+                                  weight_decay=config.weight_decay, nesterov=config.nesterov, hyper_device=hd)
     elif opt == "lion":
         K.fused_grad_lion(go, inp, w, state.m, lr=config.lr, beta1=config.beta1, beta2=config.beta2,
-                          weight_decay=config.weight_decay)
+                          weight_decay=config.weight_decay, hyper_device=hd)
     elif opt == "adamw":
         kw = dict(lr=config.lr, beta1=config.beta1, beta2=config.beta2, eps=config.eps,
-                  weight_decay=config.weight_decay, step=state.step)
+                  weight_decay=config.weight_decay, step=state.step, hyper_device=hd)
         if state.state_mode == "int8":
             K.fused_grad_adamw_int8state(go, inp, w, state.m_q, state.v_q, state.m_scale, state.v_scale,
                                          qblock=state.qblock_size, **kw)

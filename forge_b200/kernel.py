@@ -84,18 +84,23 @@ class DeviceHyper:
     """Hyper-parameters kept in device memory so that captured CUDA graphs can be replayed with a
     new lr / step: ``update(...)`` packs them on the host (same narrowing as the direct path) and
     enqueues one 64-byte copy on the current stream; pass the object as ``hyper_device=`` to the
-    fused operators."""
+    fused operators.  The pinned staging area is a small ring, so an update never overwrites bytes
+    that a copy enqueued for an earlier step may not have read yet."""
 
     NBYTES = 64
+    RING = 16
 
     def __init__(self, device):
-        self.host = torch.zeros(self.NBYTES, dtype=torch.uint8).pin_memory()
+        self.host = torch.zeros(self.RING, self.NBYTES, dtype=torch.uint8).pin_memory()
         self.dev = torch.zeros(self.NBYTES, dtype=torch.uint8, device=device)
+        self._n = 0
 
     def update(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1, momentum=0.0, nesterov=False):
         h = _hyper(lr, beta1, beta2, eps, weight_decay, step, momentum, nesterov)
-        _lib.check(_lib.load().forge_hyper_pack(ctypes.byref(h), self.host.data_ptr()), "forge_hyper_pack")
-        self.dev.copy_(self.host, non_blocking=True)
+        slot = self.host[self._n % self.RING]
+        self._n += 1
+        _lib.check(_lib.load().forge_hyper_pack(ctypes.byref(h), slot.data_ptr()), "forge_hyper_pack")
+        self.dev.copy_(slot, non_blocking=True)
         return self
 
     def data_ptr(self):
@@ -191,9 +196,9 @@ def _moment_state(m, v=None):
 # --------------------------------------------------------------------------------------------
 # reference signatures
 # --------------------------------------------------------------------------------------------
-def fused_grad_sgd(grad_output, input, weight, lr: float = 1e-3, weight_decay: float = 0.0):
+def fused_grad_sgd(grad_output, input, weight, lr: float = 1e-3, weight_decay: float = 0.0, hyper_device=None):
     """Fused weight gradient + SGD update (``kernel.py:1319-1339``): ``W = W(1 - lr wd) - lr dW``."""
-    _wgrad(grad_output, input, weight, OPT_SGD, _state(), _hyper(lr, weight_decay=weight_decay))
+    _wgrad(grad_output, input, weight, OPT_SGD, _state(), _hyper(lr, weight_decay=weight_decay), hyper_device)
 
 
 def fused_grad_adamw(grad_output, input, weight, m, v, lr: float = 1e-4, beta1: float = 0.9,
@@ -229,11 +234,11 @@ def _int8_state(weight, m_q, v_q, m_scale, v_scale, qblock, mode=ST_INT8):
 
 def fused_grad_adamw_int8state(grad_output, input, weight, m_q, v_q, m_scale, v_scale, lr: float = 1e-4,
                                beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
-                               weight_decay: float = 0.01, step: int = 1, qblock: int = 64):
+                               weight_decay: float = 0.01, step: int = 1, qblock: int = 64, hyper_device=None):
     """Fused weight gradient + AdamW with int8 moments and per-(row, qblock) fp32 absmax scales
     (``kernel.py:1487-1539``)."""
     st = _int8_state(weight, m_q, v_q, m_scale, v_scale, qblock)
-    _wgrad(grad_output, input, weight, OPT_ADAMW, st, _hyper(lr, beta1, beta2, eps, weight_decay, step))
+    _wgrad(grad_output, input, weight, OPT_ADAMW, st, _hyper(lr, beta1, beta2, eps, weight_decay, step), hyper_device)
 
 
 def optimizer_only_adamw_int8state(grad, weight, m_q, v_q, m_scale, v_scale, lr: float = 1e-4,
@@ -252,12 +257,12 @@ def _fp8_tensor_state(state):
 
 def fused_grad_adamw_fp8state(grad_output, input, weight, state, lr: float = 1e-4, beta1: float = 0.9,
                               beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.01,
-                              step: int = 1):
+                              step: int = 1, hyper_device=None):
     """Fused weight gradient + AdamW with e4m3 m / e5m2 v and one delayed scale per tensor
     (``kernel_fp8_state.py:343-392``).  ``state`` is a ``FusedOptimizerState`` in fp8 mode; the
     next-step absmax is accumulated by the kernel itself (no scratch arrays, no reduce launches)."""
     _wgrad(grad_output, input, weight, OPT_ADAMW, _fp8_tensor_state(state),
-           _hyper(lr, beta1, beta2, eps, weight_decay, step))
+           _hyper(lr, beta1, beta2, eps, weight_decay, step), hyper_device)
 
 
 def optimizer_only_adamw_fp8state(grad, weight, state, lr: float = 1e-4, beta1: float = 0.9,
@@ -283,11 +288,11 @@ def fp8_prestep(m_scale, v_scale, m_absmax_next, v_absmax_next):
 # --------------------------------------------------------------------------------------------
 def fused_grad_adamw_fp8block(grad_output, input, weight, m_q, v_q, m_scale, v_scale, lr: float = 1e-4,
                               beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
-                              weight_decay: float = 0.01, step: int = 1, qblock: int = 64):
+                              weight_decay: float = 0.01, step: int = 1, qblock: int = 64, hyper_device=None):
     """AdamW with e4m3 codes for both moments and one fp32 absmax scale per (row, 64 columns):
     the int8 scheme with ``scale = absmax / 448 + 1e-12``.  ``m_q``/``v_q`` are uint8 or float8 views."""
     st = _int8_state(weight, m_q, v_q, m_scale, v_scale, qblock, mode=ST_FP8_BLOCK)
-    _wgrad(grad_output, input, weight, OPT_ADAMW, st, _hyper(lr, beta1, beta2, eps, weight_decay, step))
+    _wgrad(grad_output, input, weight, OPT_ADAMW, st, _hyper(lr, beta1, beta2, eps, weight_decay, step), hyper_device)
 
 
 def optimizer_only_adamw_fp8block(grad, weight, m_q, v_q, m_scale, v_scale, lr: float = 1e-4,
@@ -298,12 +303,12 @@ def optimizer_only_adamw_fp8block(grad, weight, m_q, v_q, m_scale, v_scale, lr: 
 
 
 def fused_grad_sgd_momentum(grad_output, input, weight, buf, lr: float = 1e-3, momentum: float = 0.9,
-                            weight_decay: float = 0.0, nesterov: bool = False):
+                            weight_decay: float = 0.0, nesterov: bool = False, hyper_device=None):
     """SGD with momentum: ``buf = mu buf + dW``; ``u = dW + mu buf`` (Nesterov) or ``buf``;
     ``W = W(1 - lr wd) - lr u``.  Buffer semantics of ``torch.optim.SGD`` with dampening 0."""
     _require_cuda(buf)
     _wgrad(grad_output, input, weight, OPT_SGDM, _moment_state(buf),
-           _hyper(lr, weight_decay=weight_decay, momentum=momentum, nesterov=nesterov))
+           _hyper(lr, weight_decay=weight_decay, momentum=momentum, nesterov=nesterov), hyper_device)
 
 
 def optimizer_only_sgd(grad, weight, lr: float = 1e-3, weight_decay: float = 0.0):
@@ -318,11 +323,11 @@ def optimizer_only_sgd_momentum(grad, weight, buf, lr: float = 1e-3, momentum: f
 
 
 def fused_grad_lion(grad_output, input, weight, m, lr: float = 1e-4, beta1: float = 0.9,
-                    beta2: float = 0.99, weight_decay: float = 0.0):
+                    beta2: float = 0.99, weight_decay: float = 0.0, hyper_device=None):
     """Lion: ``u = sign(b1 m + (1-b1) dW)``; ``W = W(1 - lr wd) - lr u``; ``m = b2 m + (1-b2) dW``."""
     _require_cuda(m)
     _wgrad(grad_output, input, weight, OPT_LION, _moment_state(m),
-           _hyper(lr, beta1, beta2, weight_decay=weight_decay))
+           _hyper(lr, beta1, beta2, weight_decay=weight_decay), hyper_device)
 
 
 def optimizer_only_lion(grad, weight, m, lr: float = 1e-4, beta1: float = 0.9, beta2: float = 0.99,

@@ -133,6 +133,7 @@ class FusedOptimizerManager:
         self._global_step = 0
         self._micro_step = 0
         self._l2_manager = None  # accepted for signature compatibility; see the module docstring
+        self._device_hyper = {}   # optimizer type -> DeviceHyper, see enable_device_hyper
         self._fused_modules: list[FusedLinear] = []
         self._fused_module_names: dict[int, str] = {}
         self._fused_param_ids: set[int] = set()
@@ -171,9 +172,28 @@ class FusedOptimizerManager:
             if cfg is None:
                 cfg = OptimizerConfig(optimizer_type=m.optimizer_type,
                                       **{**m.optimizer_kwargs, **kwargs, "lr": lr})
+                hd = self._device_hyper.get(m.optimizer_type)
+                if hd is not None and not is_accumulating:
+                    hd.update(lr=cfg.lr, beta1=cfg.beta1, beta2=cfg.beta2, eps=cfg.eps,
+                              weight_decay=cfg.weight_decay, step=max(self._global_step, 1),
+                              momentum=cfg.momentum, nesterov=cfg.nesterov)
+                    cfg.hyper_device = hd
                 configs[key] = cfg
             m._config = cfg
             m._is_accumulating = is_accumulating
+
+    def enable_device_hyper(self, device=None):
+        """Keep the step's hyper-parameters in device memory (one 64-byte block per optimizer type,
+        rewritten by ``pre_step``) so that a CUDA graph holding the backward pass can be replayed with
+        a new lr and step count.  The step count is the manager's global step; every fused parameter
+        is assumed to be updated on every non-accumulating step.  No reference counterpart."""
+        from forge_b200.kernel import DeviceHyper
+        if device is None:
+            device = next(m.weight.device for m in self._fused_modules)
+        for m in self._fused_modules:
+            if m.optimizer_type not in self._device_hyper:
+                self._device_hyper[m.optimizer_type] = DeviceHyper(device)
+        return self
 
     def optimizer_state_dict(self) -> dict:
         modules = {}

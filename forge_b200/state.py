@@ -31,10 +31,11 @@ class OptimizerConfig:
     """Hyper-parameters of one step; build a fresh one per step so schedulers act naturally.
     Unknown keyword arguments are ignored, as in the reference (``state.py:23-24``)."""
 
-    __slots__ = ("optimizer_type", "lr", "beta1", "beta2", "eps", "weight_decay", "momentum", "nesterov")
+    __slots__ = ("optimizer_type", "lr", "beta1", "beta2", "eps", "weight_decay", "momentum", "nesterov",
+                 "hyper_device")
 
     def __init__(self, optimizer_type="adamw", lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8,
-                 weight_decay=0.01, momentum=0.0, nesterov=False, **_ignored):
+                 weight_decay=0.01, momentum=0.0, nesterov=False, hyper_device=None, **_ignored):
         self.optimizer_type = optimizer_type
         self.lr = lr
         self.beta1 = beta1
@@ -43,6 +44,9 @@ class OptimizerConfig:
         self.weight_decay = weight_decay
         self.momentum = momentum
         self.nesterov = nesterov
+        # optional forge_b200.kernel.DeviceHyper: the fused kernels then read lr / betas / step from
+        # device memory (CUDA-graph replay); the scalar fields above are ignored by them
+        self.hyper_device = hyper_device
 
     def __repr__(self):
         return ("OptimizerConfig(" + ", ".join(f"{k}={getattr(self, k)!r}" for k in self.__slots__) + ")")
