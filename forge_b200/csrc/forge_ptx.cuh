@@ -102,6 +102,10 @@ __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* gptr) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(gptr) : "memory");
+}
+
 __device__ __forceinline__ uint64_t policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
@@ -262,9 +266,65 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_
   return a;
 }
 
-// arrive on an mbarrier that may live in the other CTA of the pair (shared::cluster address)
+// Arrive on an mbarrier that may live in the other CTA of the pair (shared::cluster address).
+// Default semantics (release at CTA scope): the only thing the waiter needs ordered is this warp's
+// tensor-memory reads, which tcgen05.fence::before_thread_sync provides.  A cluster-scope release
+// made every arrive wait for the thread's outstanding global and bulk stores -- 1-2 us per tile.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// expect-tx arrive on an mbarrier of any CTA of the cluster (shared::cluster address)
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes) : "memory");
+}
+
+// 32-bit store into the shared memory of a CTA of the cluster; the bytes are counted on that CTA's
+// mbarrier, whose waiters see the value once the phase completes
+__device__ __forceinline__ void st_async_u32(uint32_t cluster_addr, uint32_t value, uint32_t cluster_bar_addr) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];" ::"r"(cluster_addr),
+               "r"(value), "r"(cluster_bar_addr)
+               : "memory");
+}
+
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Cluster launch control: a running cluster asks the hardware for the index of a cluster of this
+// grid that has not started yet and takes over its work; that cluster is then never launched.
+// The 16-byte answer lands in shared memory and completes `bar` with 16 transaction bytes.
+// After an answer that says "nothing left", no further request may be made.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void clc_try_cancel(void* response_smem, uint64_t* bar) {
+  asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];" ::"r"(
+                   smem_u32(response_smem)),
+               "r"(smem_u32(bar))
+               : "memory");
+}
+
+// true: a cluster was cancelled and `first_ctaid_x` is the blockIdx.x of its first CTA
+__device__ __forceinline__ bool clc_query(const void* response_smem, uint32_t& first_ctaid_x) {
+  uint32_t valid = 0, x = 0;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p1;\n\t"
+      ".reg .b128 resp;\n\t"
+      "ld.shared.b128 resp, [%2];\n\t"
+      "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p1, resp;\n\t"
+      "selp.u32 %1, 1, 0, p1;\n\t"
+      "@p1 clusterlaunchcontrol.query_cancel.get_first_ctaid::x.b32.b128 %0, resp;\n\t"
+      "}\n"
+      : "=r"(x), "=r"(valid)
+      : "r"(smem_u32(response_smem))
+      : "memory");
+  first_ctaid_x = x;
+  // the response buffer is written by the async proxy again on the next request
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  return valid != 0;
 }
 
 // Pair form of the tiled load: the copy lands in THIS CTA's shared memory; its transaction bytes are

@@ -12,17 +12,29 @@
 //               (BT,V) with V contiguous, X is (BT,H) with H contiguous; no transpose is made)
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), frees it
 //   warp 2      TMA producer of the W / moment sub-tiles (prefetched while the MMAs of the tile run)
-//   warp 3      idle
+//   warp 3      TMA store issuer: writes each updated sub-tile back and returns its stage to warp 2
 //   warps 4-11  epilogue: two groups of four warps; group g handles the column chunks g, g+2, ...
-//               of the 128 x 256 tile (chunks are 64 columns wide, 32 when W or the moments are
-//               fp32 and a 64-column stage would not fit twice).  Each thread owns one accumulator
-//               row: tcgen05.ld, fp32 update against the staged W/moment rows in shared memory (in
-//               place), then one TMA store per warp and tensor.
+//               of the 128 x 256 tile (chunks are 64 columns wide, 32 when a 64-column stage would
+//               not fit four times).  Each thread owns one accumulator row: tcgen05.ld, fp32 update
+//               against the staged W/moment rows in shared memory (in place), then the warp hands
+//               the chunk to warp 3.  Issuing the bulk stores from the epilogue warps themselves
+//               stalled them for 0.3-0.9 us per chunk behind the loads queued in the TMA unit.
 // The ring of state stages has an even number of slots, so the chunks of group g always land in
 // slots of parity g: every full/empty barrier then has a single consumer group that observes each
 // of its phases, which is what makes waiting on the phase parity sound.
 // Tensor memory holds two 128 x 256 fp32 accumulators, so the MMAs of tile i+1 overlap the
 // epilogue of tile i.
+//
+// Work distribution: the grid has one cluster (a CTA, or a CTA pair) per work unit, units numbered
+// row-major over the tiles.  Only as many clusters as fit on the GPU start; each of them, when it
+// has queued the loads of its unit, asks the hardware (cluster launch control) for a unit whose
+// cluster has not started yet, cancels that launch and does the unit itself.  SMs that run a
+// little slower than the others (10 % was seen) simply take fewer units, and the units in flight
+// at any moment stay neighbours in memory, so whole rows of W and of the moments stream from the
+// same DRAM pages.  The scheduler is the operand producer of the (leading) CTA; it passes unit
+// numbers to the other roles, and to the second CTA of a pair, through a four-slot queue in
+// shared memory (st.async + mbarrier).  The last `p.num_units - p.split_from` units are
+// 128-column halves of a tile: a weight with few tiles is cut that way to occupy more SMs.
 #pragma once
 
 #include "forge_ptx.cuh"
@@ -39,8 +51,8 @@ constexpr int UMMA_K = 16;
 #ifndef FORGE_OP_STAGES
 #define FORGE_OP_STAGES 3
 #endif
-#ifndef FORGE_STATE_LOAD_ROWS
-#define FORGE_STATE_LOAD_ROWS 128
+#ifndef FORGE_FILL_GATE_CHUNKS
+#define FORGE_FILL_GATE_CHUNKS 2
 #endif
 #ifndef FORGE_MAX_STATE_STAGES
 #define FORGE_MAX_STATE_STAGES 6
@@ -60,7 +72,12 @@ enum : int {
   ERR_WAIT_ST_EMPTY = 103,
   ERR_WAIT_ST_FULL = 104,
   ERR_WAIT_ACC_EMPTY = 105,
-  ERR_WAIT_ACC_FULL = 106
+  ERR_WAIT_ACC_FULL = 106,
+  ERR_WAIT_ST_DONE = 107,
+  ERR_WAIT_TQ_FULL = 108,
+  ERR_WAIT_TQ_EMPTY = 109,
+  ERR_WAIT_CLC = 110,
+  ERR_WAIT_FILL_GATE = 111
 };
 
 // Geometry of one 128-row chunk of a tensor whose rows are RB bytes wide inside the chunk.
@@ -185,7 +202,13 @@ __device__ __forceinline__ void st16_bytes(uint8_t* buf, int r, int g, const uin
 struct WgradParams {
   int BT, V, H;
   int num_kb;          // ceil(BT / BK)
-  int tiles_m, tiles_n;
+  int tiles_m;         // row tiles of TILE_M * CG rows
+  int tiles_n;         // column tiles of TILE_N columns
+  int split_from;      // units below this are whole tiles; the rest are 128-column halves of the following tiles
+  int num_units;       // = clusters in the grid
+  const uint8_t* dy;   // bf16 operands as the tensor maps see them (for the start-up L2 prefetch)
+  const uint8_t* x;
+  long long ld_dy_bytes, ld_x_bytes;
   Hyper hyper;
   float* m_scale;      // int8 / fp8-block: (V, H/64) row-major; fp8-tensor: one scalar
   float* v_scale;
@@ -231,27 +254,38 @@ struct WgradCfg {
   static_assert(kSES != 1 || kCN == 64, "one-byte codes need 64-column chunks (the quantisation block)");
 };
 
-struct alignas(8) CtrlBlock {
+constexpr int TQ_SLOTS = 4;
+
+struct alignas(16) CtrlBlock {
   uint64_t op_full[8];
   uint64_t op_empty[8];
   uint64_t st_full[6];
   uint64_t st_empty[6];
+  uint64_t st_done[6];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t tq_full[TQ_SLOTS];    // unit queue: filled by the scheduler (st.async, 4 bytes each)
+  uint64_t tq_empty[TQ_SLOTS];   // ... and drained by every other role of the cluster (leader CTA's copy is used)
+  uint64_t clc_bar;              // completion of a cluster-launch-control request
+  uint64_t fill_gate;            // operand producer -> state producer: the first unit's panel loads are all queued
+  uint4 clc_resp;                // its 16-byte answer
+  int tq_unit[TQ_SLOTS];
   uint32_t tmem_base;
   int abort_word;
 };
+static_assert(sizeof(CtrlBlock) <= 1024, "control block must fit in its reserved kilobyte");
+
+// roles other than the scheduler that read the unit queue, per CTA: MMA issuer (leader) or operand
+// producer (second CTA of a pair), state producer, store issuer, eight epilogue warps
+constexpr int TQ_READERS_PER_CTA = 3 + NUM_EPI_WARPS;
 
 // ------------------------------------------------------------------------------------------------
 template <int W_DT, int ST, int OPT, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_x,
                    const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_m,
-                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tl_w,
-                   const __grid_constant__ CUtensorMap tl_m, const __grid_constant__ CUtensorMap tl_v,
-                   const WgradParams p) {
-  // tm_w/m/v: store maps, boxes of 32 rows (one per epilogue warp); tl_w/m/v: load maps over the same
-  // tensors with boxes of 128 rows (one TMA instruction per tensor and chunk)
+                   const __grid_constant__ CUtensorMap tm_v, const WgradParams p) {
+  // tm_w/m/v: boxes of 128 rows x one swizzle row of a chunk, used for the loads and the stores
   using Cfg = WgradCfg<W_DT, ST, OPT, CG>;
   constexpr int BK = Cfg::kBK;
   constexpr int NSTAGE = Cfg::kNStage;
@@ -260,15 +294,12 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
   constexpr int SES = Cfg::kSES;
   constexpr int NMOM = Cfg::kNMom;
   constexpr int CN = Cfg::kCN;                 // columns per chunk
-  constexpr int NCH = Cfg::kNumChunks;         // chunks per tile
   constexpr int NG = CN / 16;                  // 16-column groups per chunk
   constexpr int WRB = Cfg::kWRB;
   constexpr int SRB = Cfg::kSRB;
   constexpr int WBC = BoxGeom<WRB>::kBoxRowBytes / WES;                 // columns per W box
   constexpr int SBC = (NMOM > 0) ? BoxGeom<SRB>::kBoxRowBytes / (SES > 0 ? SES : 1) : 1;
   constexpr int A_BYTES = TILE_M * BK * 2;
-  constexpr int B_COLS = TILE_N / CG;      // columns of the X panel this CTA stages
-  constexpr int B_BYTES = B_COLS * BK * 2;
   constexpr int SLAB_BYTES = 64 * BK * 2;  // one 64-element M/N slab of a K panel
 
   extern __shared__ uint8_t smem_raw[];
@@ -285,13 +316,19 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
 
   // pair mode: rank 0 of the cluster is the leader (issues the MMAs, owns op_full and acc_empty)
   const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
-  const int first_tile = (CG == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-  const int tile_stride = (CG == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int first_unit = static_cast<int>(cluster_id_x());   // == blockIdx.x / CG
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSTAGE; ++i) { mbar_init(&ctrl->op_full[i], 1); mbar_init(&ctrl->op_empty[i], 1); }
-    for (int i = 0; i < NSS; ++i) { mbar_init(&ctrl->st_full[i], 1); mbar_init(&ctrl->st_empty[i], 4); }
+    for (int i = 0; i < NSS; ++i) {
+      mbar_init(&ctrl->st_full[i], 1);
+      mbar_init(&ctrl->st_empty[i], 1);
+      mbar_init(&ctrl->st_done[i], 4);   // one arrival per warp of the group that updated the chunk
+    }
     for (int i = 0; i < 2; ++i) { mbar_init(&ctrl->acc_full[i], 1); mbar_init(&ctrl->acc_empty[i], NUM_EPI_WARPS * CG); }
+    for (int i = 0; i < TQ_SLOTS; ++i) { mbar_init(&ctrl->tq_full[i], 1); mbar_init(&ctrl->tq_empty[i], TQ_READERS_PER_CTA * CG); }
+    mbar_init(&ctrl->clc_bar, 1);
+    mbar_init(&ctrl->fill_gate, 1);
     ctrl->abort_word = 0;
     mbar_fence_init();
   }
@@ -306,9 +343,9 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
   }
   if (warp == 0 && lane == 0) { prefetch_tmap(&tm_dy); prefetch_tmap(&tm_x); }
   if (warp == 2 && lane == 0) {
-    prefetch_tmap(FORGE_STATE_LOAD_ROWS == 128 ? &tl_w : &tm_w);
-    if (NMOM > 0) prefetch_tmap(FORGE_STATE_LOAD_ROWS == 128 ? &tl_m : &tm_m);
-    if (NMOM > 1) prefetch_tmap(FORGE_STATE_LOAD_ROWS == 128 ? &tl_v : &tm_v);
+    prefetch_tmap(&tm_w);
+    if (NMOM > 0) prefetch_tmap(&tm_m);
+    if (NMOM > 1) prefetch_tmap(&tm_v);
   }
   tc_fence_before();
   __syncthreads();
@@ -316,17 +353,67 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
 
-  // p.tiles_m counts row tiles of TILE_M * CG rows; both CTAs of a pair walk the same tile list
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  // unit number -> row tile, first column, width (TILE_N, or TILE_N / 2 for a half)
+  auto decode_unit = [&](int unit, int& row_tile, int& col0, int& ncols) {
+    int tile = unit, half = 0;
+    ncols = TILE_N;
+    if (unit >= p.split_from) {
+      tile = p.split_from + ((unit - p.split_from) >> 1);
+      half = (unit - p.split_from) & 1;
+      ncols = TILE_N / 2;
+    }
+    row_tile = tile / p.tiles_n;
+    col0 = (tile - row_tile * p.tiles_n) * TILE_N + half * (TILE_N / 2);
+  };
+  // the leader CTA's tq_empty[0], where every reader of the cluster reports that it has taken a unit
+  const uint32_t tq_empty0 = (CG == 2) ? map_to_cta(smem_u32(&ctrl->tq_empty[0]), 0) : smem_u32(&ctrl->tq_empty[0]);
+  // Take the next unit from the queue (one thread of a role).  Negative: no more work, or a wait gave up.
+  uint32_t tq_pos = 0;
+  auto pop_unit = [&]() -> int {
+    const uint32_t slot = tq_pos % TQ_SLOTS;
+    if (!mbar_wait(&ctrl->tq_full[slot], (tq_pos / TQ_SLOTS) & 1, abort_word, ERR_WAIT_TQ_FULL)) return -1;
+    const int unit = *reinterpret_cast<volatile int*>(&ctrl->tq_unit[slot]);
+    if constexpr (CG == 2) mbar_arrive_cluster(tq_empty0 + slot * 8);
+    else mbar_arrive(&ctrl->tq_empty[slot]);
+    ++tq_pos;
+    return unit;
+  };
+  int row_tile, col0, ncols;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ operand producer
     if (lane == 0) {
       const uint64_t pol = policy_evict_last();
       uint32_t it = 0;
-      for (int tile = first_tile; tile < num_tiles; tile += tile_stride) {
-        const int row0 = (tile / p.tiles_n) * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
-        const int col0 = (tile % p.tiles_n) * TILE_N;
+      // the scheduler (leader) starts with the unit of its own cluster and has the next request in flight
+      int unit = first_unit;
+      bool more = true;        // the last request was answered with a unit
+      uint32_t req = 0;        // requests answered so far
+      if (cta_rank == 0) {
+        mbar_expect_tx(&ctrl->clc_bar, 16);
+        clc_try_cancel(&ctrl->clc_resp, &ctrl->clc_bar);
+      }
+      for (;;) {
+        if (cta_rank == 0) {
+          // publish `unit` (negative: the end) to the other roles of both CTAs
+          const uint32_t slot = tq_pos % TQ_SLOTS;
+          if (!mbar_wait(&ctrl->tq_empty[slot], ((tq_pos / TQ_SLOTS) & 1) ^ 1, abort_word, ERR_WAIT_TQ_EMPTY)) goto done;
+#pragma unroll
+          for (uint32_t rk = 0; rk < static_cast<uint32_t>(CG); ++rk) {
+            const uint32_t bar = (CG == 2) ? map_to_cta(smem_u32(&ctrl->tq_full[slot]), rk) : smem_u32(&ctrl->tq_full[slot]);
+            const uint32_t dst = (CG == 2) ? map_to_cta(smem_u32(&ctrl->tq_unit[slot]), rk) : smem_u32(&ctrl->tq_unit[slot]);
+            mbar_expect_tx_cluster(bar, 4);
+            st_async_u32(dst, static_cast<uint32_t>(unit), bar);
+          }
+          ++tq_pos;
+        } else {
+          unit = pop_unit();
+        }
+        if (unit < 0) break;
+        decode_unit(unit, row_tile, col0, ncols);
+        const int row0 = row_tile * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
+        const int b_cols = ncols / CG;             // columns of the X panel this CTA stages
+        const uint32_t b_bytes = static_cast<uint32_t>(b_cols) * BK * 2;
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           const int s = it % NSTAGE;
           const uint32_t ph = (it / NSTAGE) & 1;
@@ -336,22 +423,37 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           if constexpr (CG == 2) {
             // both CTAs' copies count on the LEADER's barrier; the leader expects the bytes of both
             const uint32_t full_leader = map_to_cta(smem_u32(&ctrl->op_full[s]), 0);
-            if (cta_rank == 0) mbar_expect_tx(&ctrl->op_full[s], 2 * (A_BYTES + B_BYTES));
-            const int bcol0 = col0 + static_cast<int>(cta_rank) * B_COLS;
+            if (cta_rank == 0) mbar_expect_tx(&ctrl->op_full[s], 2 * (A_BYTES + b_bytes));
+            const int bcol0 = col0 + static_cast<int>(cta_rank) * b_cols;
 #pragma unroll
             for (int i = 0; i < TILE_M / 64; ++i)
               tma_load_2d_pair(a + i * SLAB_BYTES, &tm_dy, full_leader, row0 + 64 * i, kb * BK, pol);
-#pragma unroll
-            for (int i = 0; i < B_COLS / 64; ++i)
+            for (int i = 0; i < b_cols / 64; ++i)
               tma_load_2d_pair(b + i * SLAB_BYTES, &tm_x, full_leader, bcol0 + 64 * i, kb * BK, pol);
           } else {
-            mbar_expect_tx(&ctrl->op_full[s], A_BYTES + B_BYTES);
+            mbar_expect_tx(&ctrl->op_full[s], A_BYTES + b_bytes);
 #pragma unroll
             for (int i = 0; i < TILE_M / 64; ++i)
               tma_load_2d(a + i * SLAB_BYTES, &tm_dy, &ctrl->op_full[s], row0 + 64 * i, kb * BK, pol);
-#pragma unroll
-            for (int i = 0; i < TILE_N / 64; ++i)
+            for (int i = 0; i < b_cols / 64; ++i)
               tma_load_2d(b + i * SLAB_BYTES, &tm_x, &ctrl->op_full[s], col0 + 64 * i, kb * BK, pol);
+          }
+        }
+        if (it == static_cast<uint32_t>(p.num_kb)) mbar_arrive(&ctrl->fill_gate);   // end of the first unit
+        if (cta_rank == 0) {
+          // the answer to the request made one unit ago has had a whole tile's loads to arrive
+          if (more) {
+            if (!mbar_wait(&ctrl->clc_bar, req & 1, abort_word, ERR_WAIT_CLC)) goto done;
+            ++req;
+            uint32_t first_cta = 0;
+            more = clc_query(&ctrl->clc_resp, first_cta);
+            unit = more ? static_cast<int>(first_cta / CG) : -1;
+            if (more) {
+              mbar_expect_tx(&ctrl->clc_bar, 16);
+              clc_try_cancel(&ctrl->clc_resp, &ctrl->clc_bar);
+            }
+          } else {
+            unit = -1;
           }
         }
       }
@@ -359,10 +461,12 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && cta_rank == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(TILE_M * CG, TILE_N, true, true);
+      constexpr uint32_t idesc0 = make_idesc_bf16(TILE_M * CG, 0, true, true);
       uint32_t it = 0;
       uint32_t tile_it = 0;
-      for (int tile = first_tile; tile < num_tiles; tile += tile_stride, ++tile_it) {
+      for (int unit; (unit = pop_unit()) >= 0; ++tile_it) {
+        decode_unit(unit, row_tile, col0, ncols);
+        const uint32_t idesc = idesc0 | (static_cast<uint32_t>(ncols >> 3) << 17);   // N field
         const int buf = tile_it & 1;
         const uint32_t aph = (tile_it >> 1) & 1;
         if (!mbar_wait(&ctrl->acc_empty[buf], aph ^ 1, abort_word, ERR_WAIT_ACC_EMPTY)) goto done;
@@ -400,47 +504,84 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
       // 126 us on a 14336 x 4096 bf16 update when this policy was changed).
       const uint64_t pol = policy_evict_normal();
       uint32_t q = 0;
-      for (int tile = first_tile; tile < num_tiles; tile += tile_stride) {
-        const int row0 = (tile / p.tiles_n) * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
-        const int col0 = (tile % p.tiles_n) * TILE_N;
-        for (int c = 0; c < NCH; ++c, ++q) {
+      for (int unit; (unit = pop_unit()) >= 0;) {
+        decode_unit(unit, row_tile, col0, ncols);
+        const int row0 = row_tile * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
+        const int nch = ncols / CN;
+        for (int c = 0; c < nch; ++c, ++q) {
           const int s = q % NSS;
           const uint32_t ph = (q / NSS) & 1;
           if (!mbar_wait(&ctrl->st_empty[s], ph ^ 1, abort_word, ERR_WAIT_ST_EMPTY)) goto done;
+          // Start-up: the copy engine serves requests in order and everything is cold, so a full ring
+          // of state loads ahead of the first tile's panels doubles the time to the first accumulator
+          // (8 us instead of 4).  Two chunks are enough for the epilogue to start on; the rest wait
+          // until the producer has queued the whole first panel.
+          if (q == FORGE_FILL_GATE_CHUNKS && p.num_kb > 0) {
+            if (!mbar_wait(&ctrl->fill_gate, 0, abort_word, ERR_WAIT_FILL_GATE)) goto done;
+          }
           uint8_t* wb = st_buf + s * Cfg::kStageBytes;
           mbar_expect_tx(&ctrl->st_full[s], Cfg::kStageBytes);
           const int cc = col0 + c * CN;
-          // LOAD_ROWS rows per box.  Measured on a 14336 x 4096 bf16 update at BT = 512: 128-row boxes
-          // with CTA pairs 152 us, 32-row boxes with CTA pairs 160 us, 32-row boxes with single CTAs
-          // 156 us, 128-row boxes with single CTAs 169 us.
-          constexpr int LOAD_ROWS = FORGE_STATE_LOAD_ROWS;
 #pragma unroll
-          for (int rb = 0; rb < 128 / LOAD_ROWS; ++rb) {
-            const int rr = row0 + LOAD_ROWS * rb;
-            const CUtensorMap* lw = (LOAD_ROWS == 128) ? &tl_w : &tm_w;
-            const CUtensorMap* lm = (LOAD_ROWS == 128) ? &tl_m : &tm_m;
-            const CUtensorMap* lv = (LOAD_ROWS == 128) ? &tl_v : &tm_v;
+          for (int bx = 0; bx < BoxGeom<WRB>::kBoxes; ++bx)
+            tma_load_2d(wb + bx * BoxGeom<WRB>::kBoxBytes, &tm_w, &ctrl->st_full[s], cc + bx * WBC, row0, pol);
+          if constexpr (NMOM > 0) {
+            uint8_t* mb = wb + Cfg::kWBytes;
+#pragma unroll
+            for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
+              tma_load_2d(mb + bx * BoxGeom<SRB>::kBoxBytes, &tm_m, &ctrl->st_full[s], cc + bx * SBC, row0, pol);
+          }
+          if constexpr (NMOM > 1) {
+            uint8_t* vb = wb + Cfg::kWBytes + Cfg::kSBytes;
+#pragma unroll
+            for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
+              tma_load_2d(vb + bx * BoxGeom<SRB>::kBoxBytes, &tm_v, &ctrl->st_full[s], cc + bx * SBC, row0, pol);
+          }
+        }
+      }
+    }
+  } else if (warp == 3) {
+    // ------------------------------------------------------------------ store issuer
+    if (lane == 0) {
+      // normal priority, so that the partial lines of neighbouring chunks merge in L2
+      const uint64_t pol = policy_evict_normal();
+      uint32_t q = 0;
+      for (int unit; (unit = pop_unit()) >= 0;) {
+        decode_unit(unit, row_tile, col0, ncols);
+        const int row0 = row_tile * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
+        const int nch = ncols / CN;
+        for (int c = 0; c < nch; ++c, ++q) {
+          const int s = q % NSS;
+          const uint32_t ph = (q / NSS) & 1;
+          // the four warps that updated this chunk made their writes visible to the async proxy
+          // (fence.proxy.async) before arriving
+          if (!mbar_wait(&ctrl->st_done[s], ph, abort_word, ERR_WAIT_ST_DONE)) goto done;
+          uint8_t* wb = st_buf + s * Cfg::kStageBytes;
+          const int cc = col0 + c * CN;
+          if (row0 < p.V && cc < p.H) {   // rows / columns past the edge of a started box are clipped
 #pragma unroll
             for (int bx = 0; bx < BoxGeom<WRB>::kBoxes; ++bx)
-              tma_load_2d(wb + bx * BoxGeom<WRB>::kBoxBytes + rb * LOAD_ROWS * BoxGeom<WRB>::kPitch, lw,
-                          &ctrl->st_full[s], cc + bx * WBC, rr, pol);
+              if (cc + bx * WBC < p.H) tma_store_2d(&tm_w, wb + bx * BoxGeom<WRB>::kBoxBytes, cc + bx * WBC, row0, pol);
             if constexpr (NMOM > 0) {
               uint8_t* mb = wb + Cfg::kWBytes;
 #pragma unroll
               for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-                tma_load_2d(mb + bx * BoxGeom<SRB>::kBoxBytes + rb * LOAD_ROWS * BoxGeom<SRB>::kPitch, lm,
-                            &ctrl->st_full[s], cc + bx * SBC, rr, pol);
+                if (cc + bx * SBC < p.H) tma_store_2d(&tm_m, mb + bx * BoxGeom<SRB>::kBoxBytes, cc + bx * SBC, row0, pol);
             }
             if constexpr (NMOM > 1) {
               uint8_t* vb = wb + Cfg::kWBytes + Cfg::kSBytes;
 #pragma unroll
               for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-                tma_load_2d(vb + bx * BoxGeom<SRB>::kBoxBytes + rb * LOAD_ROWS * BoxGeom<SRB>::kPitch, lv,
-                            &ctrl->st_full[s], cc + bx * SBC, rr, pol);
+                if (cc + bx * SBC < p.H) tma_store_2d(&tm_v, vb + bx * BoxGeom<SRB>::kBoxBytes, cc + bx * SBC, row0, pol);
             }
           }
+          tma_store_commit();
+          // the stage goes back to the producer as soon as the copy engine has read it
+          tma_store_wait_read<0>();
+          mbar_arrive(&ctrl->st_empty[s]);
         }
       }
+      tma_store_wait_all<0>();
     }
   } else if (warp >= EPI_WARP0) {
     // ------------------------------------------------------------------ epilogue
@@ -448,8 +589,6 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
     const int wg = (warp - EPI_WARP0) >> 2;       // 0 or 1
     const int r = quarter * 32 + lane;            // row inside the tile
     const Hyper hy = (p.hyper_dev != nullptr) ? *p.hyper_dev : p.hyper;
-    // stores: normal priority, so that the partial lines of neighbouring chunks merge in L2
-    const uint64_t pol = policy_evict_normal();
     float s_m_t = 1.0f, s_v_t = 1.0f, inv_m_t = 1.0f, inv_v_t = 1.0f;
     float amax_m_t = 0.0f, amax_v_t = 0.0f;
     if constexpr (ST == ST_FP8_TENSOR) {
@@ -459,23 +598,48 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
       inv_v_t = f_div(1.0f, s_v_t);
     }
     uint32_t tile_it = 0;
+    uint32_t q_base = 0;   // chunks of the tiles before this one (always even)
     bool ok = true;
-    int held_stage = -1;   // stage whose TMA store may still be reading shared memory
-    // Give the previous chunk's stage back to the producer.  Called a little way into the next
-    // chunk's arithmetic, by which time the TMA engine has long finished reading the stage, so the
-    // wait does not block and the stage spends almost all of its life loading or being computed on.
-    auto release_held = [&]() {
-      if (held_stage >= 0) {
-        if (lane == 0) {
-          tma_store_wait_read<0>();
-          mbar_arrive(&ctrl->st_empty[held_stage]);
+    // Start-up: nothing to update until the first accumulator is complete, and its panels are cold
+    // in L2.  With five operand stages the producer can only have five token blocks in flight, so
+    // the first tile would take three to four DRAM round trips; these 256 idle threads ask L2 for
+    // the whole panel of the first unit at once instead (the unit of a cluster's own index is known
+    // without the queue).
+    if (p.num_kb > 0) {
+      decode_unit(first_unit, row_tile, col0, ncols);
+      const int a_col0 = row_tile * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
+      const int b_cols = ncols / CG;
+      const int b_col0 = col0 + static_cast<int>(cta_rank) * ((CG == 2) ? b_cols : 0);
+      const int lines_a = TILE_M / 64, per_row = lines_a + b_cols / 64;   // 128-byte lines per token row
+      const int rows = p.BT < 1024 ? p.BT : 1024;
+      for (int idx = static_cast<int>(threadIdx.x) - EPI_WARP0 * 32; idx < rows * per_row; idx += NUM_EPI_WARPS * 32) {
+        const int row = idx / per_row, l = idx - row * per_row;
+        if (l < lines_a) {
+          const int col = a_col0 + 64 * l;
+          if (col < p.V) prefetch_l2(p.dy + row * p.ld_dy_bytes + col * 2);
+        } else {
+          const int col = b_col0 + 64 * (l - lines_a);
+          if (col < p.H) prefetch_l2(p.x + row * p.ld_x_bytes + col * 2);
         }
-        held_stage = -1;
       }
-    };
-    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride, ++tile_it) {
-      const int row0 = (tile / p.tiles_n) * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
-      const int col0 = (tile % p.tiles_n) * TILE_N;
+    }
+    for (; ok; ++tile_it) {
+      // every lane waits for the unit and reads it; one lane reports that the warp has it
+      const uint32_t slot = tq_pos % TQ_SLOTS;
+      ok = mbar_wait(&ctrl->tq_full[slot], (tq_pos / TQ_SLOTS) & 1, abort_word, ERR_WAIT_TQ_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int unit = *reinterpret_cast<volatile int*>(&ctrl->tq_unit[slot]);
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CG == 2) mbar_arrive_cluster(tq_empty0 + slot * 8);
+        else mbar_arrive(&ctrl->tq_empty[slot]);
+      }
+      ++tq_pos;
+      if (unit < 0) break;
+      decode_unit(unit, row_tile, col0, ncols);
+      const int row0 = row_tile * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
+      const int half_chunks = ncols / (2 * CN);   // chunks of this tile per epilogue group
       const int buf = tile_it & 1;
       const uint32_t aph = (tile_it >> 1) & 1;
       const int grow = row0 + r;
@@ -499,9 +663,9 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
       tc_fence_after();
 
 #pragma unroll 1
-      for (int i = 0; i < NCH / 2; ++i) {
+      for (int i = 0; i < half_chunks; ++i) {
         const int c = wg + 2 * i;
-        const uint32_t q = tile_it * NCH + c;
+        const uint32_t q = q_base + c;
         const int s = q % NSS;
         const uint32_t ph = (q / NSS) & 1;
 
@@ -517,6 +681,16 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
         ok = __all_sync(0xffffffffu, ok);
         tmem_ld_wait();
         if (!ok) break;
+        if (i == half_chunks - 1) {
+          // this warp's last read of the accumulator: hand the buffer back to the MMA issuer now,
+          // not after the update of the chunk
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&ctrl->acc_empty[buf]), 0));
+            else mbar_arrive(&ctrl->acc_empty[buf]);
+          }
+        }
         if (p.num_kb == 0) {
 #pragma unroll
           for (int k = 0; k < CN; ++k) acc[k] = 0u;
@@ -538,7 +712,6 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             for (int k = 0; k < 16; ++k) w[k] = sgd_update(w[k], __uint_as_float(acc[16 * g + k]), hy);
             store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
             if (g + 1 < NG) rw = nw;
-            if (g == 0) release_held();
           }
         } else if constexpr (OPT == OPT_SGDM || OPT == OPT_LION) {
           Raw16<WES> rw = load_raw<WES, WRB>(wb, r, 0);
@@ -562,7 +735,6 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
             store_raw<SES, SRB>(mb, r, g, pack16<SES>(m));
             if (g + 1 < NG) { rw = nw; rm = nm; }
-            if (g == 0) release_held();
           }
         } else if constexpr (ST == ST_F32 || ST == ST_BF16) {
           Raw16<WES> rw = load_raw<WES, WRB>(wb, r, 0);
@@ -588,7 +760,6 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             store_raw<SES, SRB>(mb, r, g, pack16<SES>(m));
             store_raw<SES, SRB>(vb, r, g, pack16<SES>(v));
             if (g + 1 < NG) { rw = nw; rm = nm; rv = nv; }
-            if (g == 0) release_held();
           }
         } else if constexpr (ST == ST_INT8 || ST == ST_FP8_BLOCK) {
           // The 64-column quantisation block is this thread's whole chunk row.  Pass 1 dequantises,
@@ -632,7 +803,6 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
               av = fmaxf(av, fmaxf(fabsf(v0), fabsf(v1)));
             }
             store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
-            if (g == 0) release_held();
           }
           const float sm_new = (ST == ST_INT8) ? int8_scale(am) : fp8blk_scale(am);
           const float sv_new = (ST == ST_INT8) ? int8_scale(av) : fp8blk_scale(av);
@@ -694,59 +864,17 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
             st16_bytes(mb, r, g, mo);
             st16_bytes(vb, r, g, vo);
-            if (g == 0) release_held();
           }
         }
 
-        // hand the updated rows of this warp to the TMA store engine
+        // hand the updated rows of this warp to the store issuer
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) {
-          const int rr = row0 + quarter * 32;
-          const int cc = col0 + c * CN;
-          if (rr < p.V && cc < p.H) {
-#pragma unroll
-            for (int bx = 0; bx < BoxGeom<WRB>::kBoxes; ++bx)
-              if (cc + bx * WBC < p.H)
-                tma_store_2d(&tm_w, wb + bx * BoxGeom<WRB>::kBoxBytes + quarter * 32 * BoxGeom<WRB>::kPitch,
-                             cc + bx * WBC, rr, pol);
-            if constexpr (NMOM > 0) {
-#pragma unroll
-              for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-                if (cc + bx * SBC < p.H)
-                  tma_store_2d(&tm_m, mb + bx * BoxGeom<SRB>::kBoxBytes + quarter * 32 * BoxGeom<SRB>::kPitch,
-                               cc + bx * SBC, rr, pol);
-            }
-            if constexpr (NMOM > 1) {
-#pragma unroll
-              for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-                if (cc + bx * SBC < p.H)
-                  tma_store_2d(&tm_v, vb + bx * BoxGeom<SRB>::kBoxBytes + quarter * 32 * BoxGeom<SRB>::kPitch,
-                               cc + bx * SBC, rr, pol);
-            }
-          }
-          tma_store_commit();
-          if constexpr (NSS < 4) {
-            // a group with a single stage cannot hold it across chunks
-            tma_store_wait_read<0>();
-            mbar_arrive(&ctrl->st_empty[s]);
-          }
-        }
-        release_held();                       // no-op unless the chunk had a single group
-        held_stage = (NSS >= 4) ? s : -1;
-        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctrl->st_done[s]);
       }
       if (!ok) break;
-      // all tcgen05.ld of this warp for this accumulator have completed
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&ctrl->acc_empty[buf]), 0));
-        else mbar_arrive(&ctrl->acc_empty[buf]);
-      }
+      q_base += 2 * half_chunks;
     }
-    release_held();
-    if (lane == 0) tma_store_wait_all<0>();
     if constexpr (ST == ST_FP8_TENSOR) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
@@ -762,6 +890,9 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
   }
 
 done:
+  // the single-lane roles leave their loops alone; bring every warp back together before the
+  // CTA-wide barrier (an aligned barrier executed by a diverged warp is undefined)
+  __syncwarp();
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
