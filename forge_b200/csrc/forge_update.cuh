@@ -86,6 +86,55 @@ __device__ __forceinline__ float adamw_update(float w, float g, float& m, float&
   return __fmaf_rn(w, h.decay, -q);
 }
 
+// Packed fp32 arithmetic of sm_100 on register pairs.  Written as PTX with the rounding mode spelled
+// out: an add or mul that names its rounding is never contracted into an fma, and every lane rounds
+// exactly like the scalar instruction.
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+
+// The same update on two neighbouring elements with the packed fp32 instructions of sm_100
+// (each lane rounds exactly like the scalar form, so the results are
+// bit-identical to adamw_update); halves the instruction count of everything but the two
+// special-function evaluations.
+__device__ __forceinline__ float2 adamw_update2(float2 w, float2 g, float2& m, float2& v, const Hyper& h) {
+  const float2 b1 = make_float2(h.beta1, h.beta1), c1 = make_float2(h.one_m_beta1, h.one_m_beta1);
+  const float2 b2 = make_float2(h.beta2, h.beta2), c2 = make_float2(h.one_m_beta2, h.one_m_beta2);
+  // The products are packed; the sums are scalar adds.  A packed add fed by a packed multiply came
+  // out of the assembler as one fused operation (m', v' off by an ulp in 5 % of the elements), and
+  // the moments must match the separately rounded reference arithmetic bit for bit.
+  const float2 pm = fmul2(b1, m), pg = fmul2(c1, g);
+  m = make_float2(f_add(pm.x, pg.x), f_add(pm.y, pg.y));
+  const float2 pv = fmul2(b2, v), pgg = fmul2(fmul2(c2, g), g);
+  v = make_float2(f_add(pv.x, pgg.x), f_add(pv.y, pgg.y));
+  const float2 vh = fmul2(v, make_float2(h.inv_bc2, h.inv_bc2));
+  const float2 den = fadd2(make_float2(sqrt_approx(vh.x), sqrt_approx(vh.y)), make_float2(h.eps, h.eps));
+  const float2 mh = fmul2(m, make_float2(-h.lr_over_bc1, -h.lr_over_bc1));
+  const float2 nq = fmul2(mh, make_float2(rcp_approx(den.x), rcp_approx(den.y)));
+  return ffma2(w, make_float2(h.decay, h.decay), nq);
+}
+
 // SGD with decoupled decay: w' = w (1 - lr wd) - lr g
 __device__ __forceinline__ float sgd_update(float w, float g, const Hyper& h) {
   return f_sub(f_mul(w, h.decay), f_mul(h.lr, g));
@@ -125,6 +174,33 @@ __device__ __forceinline__ uint32_t int8_code_bits(float x, float scale, float r
   asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(div_by_rcp(x, scale, rscale)));
   return static_cast<uint32_t>(q) & 0xFFu;
 }
+// ---- the same quantiser arithmetic on element pairs, without the conversion unit ----------------
+// Correctly rounded a / b on two elements given neg_b = -b and rb = RN(1 / b) (div_by_rcp, packed).
+__device__ __forceinline__ float2 div2_by_rcp(float2 a, float2 neg_b, float2 rb) {
+  const float2 q = fmul2(a, rb);
+  const float2 r = ffma2(q, neg_b, a);
+  return ffma2(r, rb, q);
+}
+// Two int8 codes -> fp32, exactly.  `biased` holds four codes with their sign bits flipped
+// (code + 128 as an unsigned byte); a byte dropped into the mantissa of 2^23 reads as 2^23 + byte,
+// and subtracting 2^23 + 128 leaves the code.  `first` is 0 or 2 (which pair of the word).
+__device__ __forceinline__ float2 int8x2_to_float(uint32_t biased, int first) {
+  const float f0 = __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7540u + first));
+  const float f1 = __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7541u + first));
+  return fadd2(make_float2(f0, f1), make_float2(-8388736.0f, -8388736.0f));
+}
+// rint() of two quotients as the low bytes of q + 1.5 * 2^23 (round to nearest even; two's
+// complement in the mantissa).  |q| < 127.5 by construction of the scale, so no clamp is needed.
+// Returns the two sums; int8x4_pack gathers their low bytes.
+__device__ __forceinline__ float2 int8x2_round(float2 q) {
+  return fadd2(q, make_float2(12582912.0f, 12582912.0f));
+}
+__device__ __forceinline__ uint32_t int8x4_pack(float2 r01, float2 r23) {
+  const uint32_t lo = __byte_perm(__float_as_uint(r01.x), __float_as_uint(r01.y), 0x0040u);
+  const uint32_t hi = __byte_perm(__float_as_uint(r23.x), __float_as_uint(r23.y), 0x0040u);
+  return __byte_perm(lo, hi, 0x5410u);
+}
+
 // two e4m3 codes at once (round to nearest even, saturate to +-448): low byte = lo, next byte = hi
 __device__ __forceinline__ uint32_t e4m3x2_code_bits(float lo, float hi) {
   uint16_t r;

@@ -754,8 +754,15 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             unpack16<SES>(rm, m);
             unpack16<SES>(rv, v);
 #pragma unroll
-            for (int k = 0; k < 16; ++k)
-              w[k] = adamw_update(w[k], __uint_as_float(acc[16 * g + k]), m[k], v[k], hy);
+            for (int k = 0; k < 16; k += 2) {
+              float2 m2 = make_float2(m[k], m[k + 1]), v2 = make_float2(v[k], v[k + 1]);
+              const float2 w2 = adamw_update2(make_float2(w[k], w[k + 1]),
+                                              make_float2(__uint_as_float(acc[16 * g + k]), __uint_as_float(acc[16 * g + k + 1])),
+                                              m2, v2, hy);
+              w[k] = w2.x; w[k + 1] = w2.y;
+              m[k] = m2.x; m[k + 1] = m2.y;
+              v[k] = v2.x; v[k + 1] = v2.y;
+            }
             store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
             store_raw<SES, SRB>(mb, r, g, pack16<SES>(m));
             store_raw<SES, SRB>(vb, r, g, pack16<SES>(v));
@@ -768,6 +775,7 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           // the new scale.  No shuffles, no recomputation.
           const float sm_old = (i == 0) ? sc_m[0] : sc_m[1];
           const float sv_old = (i == 0) ? sc_v[0] : sc_v[1];
+          const float2 sm_old2 = make_float2(sm_old, sm_old), sv_old2 = make_float2(sv_old, sv_old);
           float mm[CN], vv[CN];
           float am = 0.0f, av = 0.0f;
 #pragma unroll
@@ -777,52 +785,61 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             unpack16<WES>(load_raw<WES, WRB>(wb, r, g), w);
             ld16_bytes(mb, r, g, mq);
             ld16_bytes(vb, r, g, vq);
+            if constexpr (ST == ST_INT8) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) { mq[j] ^= 0x80808080u; vq[j] ^= 0x80808080u; }
+            }
 #pragma unroll
             for (int k = 0; k < 16; k += 2) {
-              float m0, m1, v0, v1;
+              float2 m2, v2;
               if constexpr (ST == ST_INT8) {
-                m0 = static_cast<float>(static_cast<int>(static_cast<int8_t>(mq[k >> 2] >> (8 * (k & 3)))));
-                m1 = static_cast<float>(static_cast<int>(static_cast<int8_t>(mq[k >> 2] >> (8 * ((k + 1) & 3)))));
-                v0 = static_cast<float>(static_cast<int>(static_cast<int8_t>(vq[k >> 2] >> (8 * (k & 3)))));
-                v1 = static_cast<float>(static_cast<int>(static_cast<int8_t>(vq[k >> 2] >> (8 * ((k + 1) & 3)))));
+                m2 = int8x2_to_float(mq[k >> 2], k & 3);
+                v2 = int8x2_to_float(vq[k >> 2], k & 3);
               } else {
-                e4m3x2_to_float(mq[k >> 2] >> (8 * (k & 3)), m0, m1);
-                e4m3x2_to_float(vq[k >> 2] >> (8 * (k & 3)), v0, v1);
+                e4m3x2_to_float(mq[k >> 2] >> (8 * (k & 3)), m2.x, m2.y);
+                e4m3x2_to_float(vq[k >> 2] >> (8 * (k & 3)), v2.x, v2.y);
               }
-              m0 = f_mul(m0, sm_old);
-              m1 = f_mul(m1, sm_old);
-              v0 = fmaxf(f_mul(v0, sv_old), 1e-8f);
-              v1 = fmaxf(f_mul(v1, sv_old), 1e-8f);
-              w[k] = adamw_update(w[k], __uint_as_float(acc[16 * g + k]), m0, v0, hy);
-              w[k + 1] = adamw_update(w[k + 1], __uint_as_float(acc[16 * g + k + 1]), m1, v1, hy);
-              mm[16 * g + k] = m0;
-              mm[16 * g + k + 1] = m1;
-              vv[16 * g + k] = v0;
-              vv[16 * g + k + 1] = v1;
-              am = fmaxf(am, fmaxf(fabsf(m0), fabsf(m1)));
-              av = fmaxf(av, fmaxf(fabsf(v0), fabsf(v1)));
+              m2 = fmul2(m2, sm_old2);
+              v2 = fmul2(v2, sv_old2);
+              v2.x = fmaxf(v2.x, 1e-8f);
+              v2.y = fmaxf(v2.y, 1e-8f);
+              const float2 w2 = adamw_update2(make_float2(w[k], w[k + 1]),
+                                              make_float2(__uint_as_float(acc[16 * g + k]), __uint_as_float(acc[16 * g + k + 1])),
+                                              m2, v2, hy);
+              w[k] = w2.x;
+              w[k + 1] = w2.y;
+              mm[16 * g + k] = m2.x;
+              mm[16 * g + k + 1] = m2.y;
+              vv[16 * g + k] = v2.x;
+              vv[16 * g + k + 1] = v2.y;
+              am = fmaxf(am, fmaxf(fabsf(m2.x), fabsf(m2.y)));
+              av = fmaxf(av, fmaxf(fabsf(v2.x), fabsf(v2.y)));
             }
             store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
           }
           const float sm_new = (ST == ST_INT8) ? int8_scale(am) : fp8blk_scale(am);
           const float sv_new = (ST == ST_INT8) ? int8_scale(av) : fp8blk_scale(av);
           const float rsm = f_div(1.0f, sm_new), rsv = f_div(1.0f, sv_new);
+          const float2 nsm2 = make_float2(-sm_new, -sm_new), nsv2 = make_float2(-sv_new, -sv_new);
+          const float2 rsm2 = make_float2(rsm, rsm), rsv2 = make_float2(rsv, rsv);
 #pragma unroll
           for (int g = 0; g < NG; ++g) {
-            uint32_t mo[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
+            uint32_t mo[4], vo[4];
 #pragma unroll
-            for (int k = 0; k < 16; k += 2) {
-              uint32_t mc, vc;
+            for (int j = 0; j < 4; ++j) {
+              const int k = 16 * g + 4 * j;
+              const float2 qm01 = div2_by_rcp(make_float2(mm[k], mm[k + 1]), nsm2, rsm2);
+              const float2 qm23 = div2_by_rcp(make_float2(mm[k + 2], mm[k + 3]), nsm2, rsm2);
+              const float2 qv01 = div2_by_rcp(make_float2(vv[k], vv[k + 1]), nsv2, rsv2);
+              const float2 qv23 = div2_by_rcp(make_float2(vv[k + 2], vv[k + 3]), nsv2, rsv2);
               if constexpr (ST == ST_INT8) {
-                mc = int8_code_bits(mm[16 * g + k], sm_new, rsm) | (int8_code_bits(mm[16 * g + k + 1], sm_new, rsm) << 8);
-                vc = int8_code_bits(vv[16 * g + k], sv_new, rsv) | (int8_code_bits(vv[16 * g + k + 1], sv_new, rsv) << 8);
+                mo[j] = int8x4_pack(int8x2_round(qm01), int8x2_round(qm23));
+                vo[j] = int8x4_pack(int8x2_round(qv01), int8x2_round(qv23));
               } else {
                 // |x / scale| < 448.5 by construction of the scale, and the conversion saturates
-                mc = e4m3x2_code_bits(div_by_rcp(mm[16 * g + k], sm_new, rsm), div_by_rcp(mm[16 * g + k + 1], sm_new, rsm));
-                vc = e4m3x2_code_bits(div_by_rcp(vv[16 * g + k], sv_new, rsv), div_by_rcp(vv[16 * g + k + 1], sv_new, rsv));
+                mo[j] = e4m3x2_code_bits(qm01.x, qm01.y) | (e4m3x2_code_bits(qm23.x, qm23.y) << 16);
+                vo[j] = e4m3x2_code_bits(qv01.x, qv01.y) | (e4m3x2_code_bits(qv23.x, qv23.y) << 16);
               }
-              mo[k >> 2] |= mc << (8 * (k & 3));
-              vo[k >> 2] |= vc << (8 * (k & 3));
             }
             st16_bytes(mb, r, g, mo);
             st16_bytes(vb, r, g, vo);
@@ -844,22 +861,25 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             ld16_bytes(vb, r, g, vq);
 #pragma unroll
             for (int k = 0; k < 16; k += 2) {
-              float m0, m1, v0, v1;
-              e4m3x2_to_float(mq[k >> 2] >> (8 * (k & 3)), m0, m1);
-              e5m2x2_to_float(vq[k >> 2] >> (8 * (k & 3)), v0, v1);
-              m0 = f_mul(m0, s_m_t);
-              m1 = f_mul(m1, s_m_t);
-              v0 = f_mul(v0, s_v_t);
-              v1 = f_mul(v1, s_v_t);
-              w[k] = adamw_update(w[k], __uint_as_float(acc[16 * g + k]), m0, v0, hy);
-              w[k + 1] = adamw_update(w[k + 1], __uint_as_float(acc[16 * g + k + 1]), m1, v1, hy);
+              float2 m2, v2;
+              e4m3x2_to_float(mq[k >> 2] >> (8 * (k & 3)), m2.x, m2.y);
+              e5m2x2_to_float(vq[k >> 2] >> (8 * (k & 3)), v2.x, v2.y);
+              m2 = fmul2(m2, make_float2(s_m_t, s_m_t));
+              v2 = fmul2(v2, make_float2(s_v_t, s_v_t));
+              const float2 w2 = adamw_update2(make_float2(w[k], w[k + 1]),
+                                              make_float2(__uint_as_float(acc[16 * g + k]), __uint_as_float(acc[16 * g + k + 1])),
+                                              m2, v2, hy);
+              w[k] = w2.x;
+              w[k + 1] = w2.y;
               // rows / columns beyond the matrix hold zeros (zero-filled loads), so they never raise
               // the running maxima
-              amax_m_t = fmaxf(amax_m_t, fmaxf(fabsf(m0), fabsf(m1)));
-              amax_v_t = fmaxf(amax_v_t, fmaxf(fabsf(v0), fabsf(v1)));
+              amax_m_t = fmaxf(amax_m_t, fmaxf(fabsf(m2.x), fabsf(m2.y)));
+              amax_v_t = fmaxf(amax_v_t, fmaxf(fabsf(v2.x), fabsf(v2.y)));
               // the conversions saturate to +-448 / +-57344, which is the reference's clamp
-              mo[k >> 2] |= e4m3x2_code_bits(f_mul(m0, inv_m_t), f_mul(m1, inv_m_t)) << (8 * (k & 3));
-              vo[k >> 2] |= e5m2x2_code_bits(f_mul(v0, inv_v_t), f_mul(v1, inv_v_t)) << (8 * (k & 3));
+              const float2 mc = fmul2(m2, make_float2(inv_m_t, inv_m_t));
+              const float2 vc = fmul2(v2, make_float2(inv_v_t, inv_v_t));
+              mo[k >> 2] |= e4m3x2_code_bits(mc.x, mc.y) << (8 * (k & 3));
+              vo[k >> 2] |= e5m2x2_code_bits(vc.x, vc.y) << (8 * (k & 3));
             }
             store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
             st16_bytes(mb, r, g, mo);

@@ -309,6 +309,45 @@ def test_fused_equals_unfused_twin_bitwise():
         assert torch.equal(a.view(torch.int16), b.view(torch.int16))
 
 
+@pytest.mark.parametrize("V,H", [(14336, 4096), (4096, 14336), (4096, 4096), (1024, 4096)])
+@pytest.mark.parametrize("mode", ["bf16", "int8"])
+def test_full_size_fused_equals_unfused_twin(V, H, mode):
+    """The Llama-3.1-8B projection shapes at BT = 512 (many rounds of work units per SM pair, the
+    half-tile tail, every tile of the weight): the fused update equals, bit for bit, the
+    optimizer-only kernel fed the gradient that the SGD variant of the same mainloop reveals."""
+    BT = 512
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    dyd = (torch.randn(BT, V, device=DEV, generator=gen) * 1e-2).bfloat16()
+    xd = torch.randn(BT, H, device=DEV, generator=gen).bfloat16()
+    w0 = (torch.randn(V, H, device=DEV, generator=gen) * 0.02).bfloat16()
+    gneg = torch.zeros(V, H, device=DEV)
+    K.fused_grad_sgd(dyd, xd, gneg, lr=1.0, weight_decay=0.0)   # fp32 W = 0: stores -g unrounded
+    grad = (-gneg).contiguous()
+    del gneg
+    if mode == "bf16":
+        m0 = (torch.randn(V, H, device=DEV, generator=gen) * 1e-3).bfloat16()
+        v0 = (torch.randn(V, H, device=DEV, generator=gen).abs() * 1e-5).bfloat16()
+        fused = (w0.clone(), m0.clone(), v0.clone())
+        twin = (w0.clone(), m0.clone(), v0.clone())
+        K.fused_grad_adamw(dyd, xd, *fused, **ADAMW)
+        K.optimizer_only_adamw(grad, *twin, **ADAMW)
+    else:
+        mq = torch.randint(-127, 128, (V, H), device=DEV, generator=gen, dtype=torch.int8)
+        vq = torch.randint(0, 128, (V, H), device=DEV, generator=gen, dtype=torch.int8)
+        ms = torch.rand(V, H // 64, device=DEV, generator=gen) * 1e-5 + 1e-6
+        vs = torch.rand(V, H // 64, device=DEV, generator=gen) * 1e-9 + 1e-10
+        fused = (w0.clone(), mq.clone(), vq.clone(), ms.clone(), vs.clone())
+        twin = (w0.clone(), mq.clone(), vq.clone(), ms.clone(), vs.clone())
+        K.fused_grad_adamw_int8state(dyd, xd, *fused, **ADAMW)
+        K.optimizer_only_adamw_int8state(grad, *twin, **ADAMW)
+    torch.cuda.synchronize()
+    assert not torch.equal(fused[0], w0)
+    for name, a, b in zip(("W", "m", "v", "m_scale", "v_scale"), fused, twin):
+        ai = a.view(torch.int16 if a.dtype == torch.bfloat16 else (torch.int32 if a.dtype == torch.float32 else torch.int8))
+        bi = b.view(ai.dtype)
+        assert torch.equal(ai, bi), f"{name}: {(ai != bi).sum().item()} of {ai.numel()} elements differ"
+
+
 # ------------------------------------------------------------------ fp32 operands, edge cases, errors
 @pytest.mark.parametrize("BT,V,H", [(128, 256, 128), (64, 512, 256), (256, 1024, 512), (50, 136, 264)])
 def test_fp32_operands_close_to_fp32_oracle(BT, V, H):
