@@ -204,9 +204,19 @@ def run_forge(args):
     for name, V, H, grp in linears:
         r0, r1 = row_range(V, rank, shard_world)
         w = torch.empty(r1 - r0, H, dtype=torch.bfloat16, device=dev).normal_(0.0, 0.02, generator=gen)
-        m = torch.zeros_like(w)
-        v = torch.zeros_like(w)
+        if args.moments == "int8":       # codes 0, scales 1: the reference's initial state (state.py:108-117)
+            m = (torch.zeros(r1 - r0, H, dtype=torch.int8, device=dev), torch.ones(r1 - r0, H // 64, device=dev))
+            v = (torch.zeros(r1 - r0, H, dtype=torch.int8, device=dev), torch.ones(r1 - r0, H // 64, device=dev))
+        else:
+            m = torch.zeros_like(w)
+            v = torch.zeros_like(w)
         params.append((name, V, H, grp, r0, r1, w, m, v))
+
+    def update(dy, x, w, m, v):
+        if args.moments == "int8":
+            K.fused_grad_adamw_int8state(dy, x, w, m[0], v[0], m[1], v[1], hyper_device=hyper_dev)
+        else:
+            K.fused_grad_adamw(dy, x, w, m, v, hyper_device=hyper_dev)
 
     # activations: one X per distinct in-features (feature shard when N > 1), one dY per distinct V_r
     x_full, x_shard, dys = {}, {}, {}
@@ -273,7 +283,7 @@ def run_forge(args):
             else:
                 x = x_full[H]
             with torch.cuda.stream(st):
-                K.fused_grad_adamw(dys[r1 - r0], x, w, m, v, hyper_device=hyper_dev)
+                update(dys[r1 - r0], x, w, m, v)
         for st in side_streams + ([comm_stream] if do_gather else []):
             done = torch.cuda.Event()
             done.record(st)
@@ -312,7 +322,7 @@ def run_forge(args):
                 x = staged(x_full[H], "x")
                 x.copy_(x_h, non_blocking=True)
                 h2d += x_h.numel() * 2
-            K.fused_grad_adamw(dy_d, x, w, m, v, hyper_device=hyper_dev)
+            update(dy_d, x, w, m, v)
         # the step's result: the device status word and one updated weight, read back to the host
         host_result[0:1].copy_(_lib.status_word(dev)[0:1].float(), non_blocking=True)
         host_result[1:2].copy_(params[-1][6][0, 0:1].float(), non_blocking=True)
@@ -410,14 +420,15 @@ def run_forge(args):
         peaks, peak_kind = measured_peaks()
         launches = len(params)
         # algorithmic bytes this rank moves per step (row shard of the state, full X, dY slice)
-        alg = sum(algorithmic_bytes(r1 - r0, H) for _, V, H, _, r0, r1, *_ in params)
+        state_bytes = 6 if args.moments == "bf16" else 4 + 2 * 4 / 64   # per element: W + m + v (+ scales)
+        alg = sum(algorithmic_bytes(r1 - r0, H, state_bytes=state_bytes) for _, V, H, _, r0, r1, *_ in params)
         achieved = alg / (ms_dev * 1e-3) / 1e9
         flops = sum(2 * BT * (r1 - r0) * H for _, V, H, _, r0, r1, *_ in params)
         line = {
             "metric": "fused_wgrad_adamw_ms_per_step", "value": ms_dev, "unit": "ms/step", "n_gpus": world,
             "steps": args.steps, "warmup": W, "ms_per_step": ms_dev, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "bt": BT, "linears": launches, "weights": "bf16", "moments": "bf16",
+            "config": {"workload": args.workload, "bt": BT, "linears": launches, "weights": "bf16", "moments": args.moments,
                        "optimizer": "adamw", "launch": "cuda_graph" if g_dev is not None else "eager", "streams": n_streams,
                        "parallelism": (f"tp{world}-rows" + ("+gather-x" if do_gather else "")) if world > 1 else "single",
                        "l2": "each weight and its moments are distinct buffers (45 GB in total), so every launch "
@@ -425,11 +436,11 @@ def run_forge(args):
                        "parameters": sum(V * H for _, V, H, *_ in params)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
-                         "kernel": "forge_wgrad_kernel<bf16 W, bf16 moments, AdamW>",
+                         "kernel": f"forge_wgrad_kernel<bf16 W, {args.moments} moments, AdamW>",
                          "algorithmic_bytes_per_launch": alg / launches, "avg_launch_us": ms_dev * 1e3 / launches,
                          "tflops": flops / (ms_dev * 1e-3) / 1e12,
                          # dram read+write per launch from the ncu capture in profiles/, scaled by bytes
-                         "traffic": TRAFFIC_RATIO * alg / launches if TRAFFIC_RATIO else None},
+                         "traffic": TRAFFIC_RATIO * alg / launches if (TRAFFIC_RATIO and args.moments == "bf16") else None},
             "e2e": {"value": ms_e2e, "unit": "ms/step", "h2d_bytes_per_step": moved[0], "d2h_bytes_per_step": moved[1],
                     "steps": e2e_steps},
             "gpu_launches": launches * args.steps,
@@ -492,6 +503,8 @@ def main():
     ap.add_argument("--impl", default="forge", choices=["forge", "reference"])
     ap.add_argument("--workload", default="llama3.1-8b-linears")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--moments", default="bf16", choices=["bf16", "int8"],
+                    help="storage of the AdamW moments (int8: per-(row, 64 columns) absmax scales)")
     ap.add_argument("--streams", type=int, default=4, help="streams the independent updates of a step are spread over")
     ap.add_argument("--gather-x", action="store_true",
                     help="N > 1: all-gather the feature-sharded X by NCCL inside the timed step")
