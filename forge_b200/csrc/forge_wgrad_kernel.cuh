@@ -508,6 +508,18 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
         decode_unit(unit, row_tile, col0, ncols);
         const int row0 = row_tile * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
         const int nch = ncols / CN;
+        if constexpr (ST == ST_INT8 || ST == ST_FP8_BLOCK) {
+          // The epilogue threads read their rows' block scales straight from global memory at the top
+          // of a tile; this thread knows the tile several microseconds earlier and pulls the lines
+          // into L2 (one 16-byte group of scales per row, tensor and tile).
+          for (int rr = 0; rr < TILE_M; ++rr) {
+            if (row0 + rr < p.V) {
+              const size_t off = static_cast<size_t>(row0 + rr) * p.ld_scale + (col0 >> 6);
+              prefetch_l2(p.m_scale + off);
+              prefetch_l2(p.v_scale + off);
+            }
+          }
+        }
         for (int c = 0; c < nch; ++c, ++q) {
           const int s = q % NSS;
           const uint32_t ph = (q / NSS) & 1;
@@ -681,7 +693,8 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
         ok = __all_sync(0xffffffffu, ok);
         tmem_ld_wait();
         if (!ok) break;
-        if (i == half_chunks - 1) {
+        constexpr bool kTmemScratch = (ST == ST_INT8 || ST == ST_FP8_BLOCK);
+        if (!kTmemScratch && i == half_chunks - 1) {
           // this warp's last read of the accumulator: hand the buffer back to the MMA issuer now,
           // not after the update of the chunk
           tc_fence_before();
@@ -770,18 +783,22 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           }
         } else if constexpr (ST == ST_INT8 || ST == ST_FP8_BLOCK) {
           // The 64-column quantisation block is this thread's whole chunk row.  Pass 1 dequantises,
-          // updates W and keeps the new moments in registers (they replace the accumulator values
-          // they were computed from) while tracking the block absmax; pass 2 requantises them with
-          // the new scale.  No shuffles, no recomputation.
+          // updates W and tracks the block absmax; the new second moments stay in registers (they
+          // replace the accumulator values they were computed from), the new first moments are
+          // parked in the accumulator's own tensor-memory columns, which this thread has already
+          // read (holding both in registers spilled).  Pass 2 requantises them with the new scale.
+          // No shuffles, no recomputation.
           const float sm_old = (i == 0) ? sc_m[0] : sc_m[1];
           const float sv_old = (i == 0) ? sc_v[0] : sc_v[1];
           const float2 sm_old2 = make_float2(sm_old, sm_old), sv_old2 = make_float2(sv_old, sv_old);
-          float mm[CN], vv[CN];
+          const uint32_t scratch = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(buf * TILE_N + c * CN);
+          float vv[CN];
           float am = 0.0f, av = 0.0f;
 #pragma unroll
           for (int g = 0; g < NG; ++g) {
             float w[16];
-            uint32_t mq[4], vq[4];
+            uint32_t mq[4], vq[4], mnew[16];
             unpack16<WES>(load_raw<WES, WRB>(wb, r, g), w);
             ld16_bytes(mb, r, g, mq);
             ld16_bytes(vb, r, g, vq);
@@ -808,30 +825,36 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
                                               m2, v2, hy);
               w[k] = w2.x;
               w[k + 1] = w2.y;
-              mm[16 * g + k] = m2.x;
-              mm[16 * g + k + 1] = m2.y;
+              mnew[k] = __float_as_uint(m2.x);
+              mnew[k + 1] = __float_as_uint(m2.y);
               vv[16 * g + k] = v2.x;
               vv[16 * g + k + 1] = v2.y;
               am = fmaxf(am, fmaxf(fabsf(m2.x), fabsf(m2.y)));
               av = fmaxf(av, fmaxf(fabsf(v2.x), fabsf(v2.y)));
             }
+            tmem_st_32x16(scratch + 16 * g, mnew);
             store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
           }
+          tmem_st_wait();
           const float sm_new = (ST == ST_INT8) ? int8_scale(am) : fp8blk_scale(am);
           const float sv_new = (ST == ST_INT8) ? int8_scale(av) : fp8blk_scale(av);
           const float rsm = f_div(1.0f, sm_new), rsv = f_div(1.0f, sv_new);
           const float2 nsm2 = make_float2(-sm_new, -sm_new), nsv2 = make_float2(-sv_new, -sv_new);
           const float2 rsm2 = make_float2(rsm, rsm), rsv2 = make_float2(rsv, rsv);
+          uint32_t mcur[16];
+          tmem_ld_32x16(scratch, mcur);
 #pragma unroll
           for (int g = 0; g < NG; ++g) {
-            uint32_t mo[4], vo[4];
+            uint32_t mo[4], vo[4], mnext[16];
+            tmem_ld_wait();
+            if (g + 1 < NG) tmem_ld_32x16(scratch + 16 * (g + 1), mnext);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const int k = 16 * g + 4 * j;
-              const float2 qm01 = div2_by_rcp(make_float2(mm[k], mm[k + 1]), nsm2, rsm2);
-              const float2 qm23 = div2_by_rcp(make_float2(mm[k + 2], mm[k + 3]), nsm2, rsm2);
-              const float2 qv01 = div2_by_rcp(make_float2(vv[k], vv[k + 1]), nsv2, rsv2);
-              const float2 qv23 = div2_by_rcp(make_float2(vv[k + 2], vv[k + 3]), nsv2, rsv2);
+              const int k = 4 * j;
+              const float2 qm01 = div2_by_rcp(make_float2(__uint_as_float(mcur[k]), __uint_as_float(mcur[k + 1])), nsm2, rsm2);
+              const float2 qm23 = div2_by_rcp(make_float2(__uint_as_float(mcur[k + 2]), __uint_as_float(mcur[k + 3])), nsm2, rsm2);
+              const float2 qv01 = div2_by_rcp(make_float2(vv[16 * g + k], vv[16 * g + k + 1]), nsv2, rsv2);
+              const float2 qv23 = div2_by_rcp(make_float2(vv[16 * g + k + 2], vv[16 * g + k + 3]), nsv2, rsv2);
               if constexpr (ST == ST_INT8) {
                 mo[j] = int8x4_pack(int8x2_round(qm01), int8x2_round(qm23));
                 vo[j] = int8x4_pack(int8x2_round(qv01), int8x2_round(qv23));
@@ -843,6 +866,19 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             }
             st16_bytes(mb, r, g, mo);
             st16_bytes(vb, r, g, vo);
+            if (g + 1 < NG) {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) mcur[k] = mnext[k];
+            }
+          }
+          if (i == half_chunks - 1) {
+            // last use of this accumulator buffer (as scratch): hand it back to the MMA issuer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&ctrl->acc_empty[buf]), 0));
+              else mbar_arrive(&ctrl->acc_empty[buf]);
+            }
           }
           {
             const int cb = (col0 >> 6) + c;
