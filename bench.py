@@ -299,35 +299,65 @@ def run_forge(args):
 
     host_result = torch.zeros(2, dtype=torch.float32).pin_memory()
 
+    copy_stream = torch.cuda.Stream()
+    last_use = {}     # staging buffer -> event after the kernel that last read it
+
     def step_host(step_no=None, sync=True):
-        """Same step, inputs start in pinned host memory; returns H2D / D2H bytes moved."""
+        """Same step, inputs start in pinned host memory; returns H2D / D2H bytes moved.  The copies of
+        launch i+1 run on a second stream while launch i computes (two staging sets per shape)."""
+        main = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(main)
+        copy_stream.wait_event(start)     # orders this step's copies after the previous step's kernels
+        last_use.clear()
         h2d = 0
         last_grp, xg = None, None
-        for name, V, H, grp, r0, r1, w, m, v in params:
-            dy_h = pinned(dys[r1 - r0])
-            dy_d = staged(dys[r1 - r0], "dy")
-            dy_d.copy_(dy_h, non_blocking=True)
-            h2d += dy_h.numel() * 2
+
+        def upload(src_dev, tag, slot):
+            nonlocal h2d
+            src_h = pinned(src_dev)
+            dst = staged(src_dev, (tag, slot))
+            with torch.cuda.stream(copy_stream):
+                ev = last_use.get(dst.data_ptr())
+                if ev is not None:
+                    copy_stream.wait_event(ev)
+                dst.copy_(src_h, non_blocking=True)
+            h2d += src_h.numel() * 2
+            return dst
+
+        for i, (name, V, H, grp, r0, r1, w, m, v) in enumerate(params):
+            slot = i & 1
+            dy_d = upload(dys[r1 - r0], "dy", slot)
             if do_gather:
-                if grp != last_grp:
-                    xs_h = pinned(x_shard[H])
-                    xs_d = staged(x_shard[H], "x")
-                    xs_d.copy_(xs_h, non_blocking=True)
-                    h2d += xs_h.numel() * 2
+                new_grp = grp != last_grp
+                xs_d = upload(x_shard[H], "x", slot) if new_grp else None
+            else:
+                x = upload(x_full[H], "x", slot)
+            ready = torch.cuda.Event()
+            ready.record(copy_stream)
+            main.wait_event(ready)
+            used = [dy_d]
+            if do_gather:
+                if new_grp:
                     xg = all_gather_features(xs_d)
+                    used.append(xs_d)
                     last_grp = grp
                 x = xg
             else:
-                x_h = pinned(x_full[H])
-                x = staged(x_full[H], "x")
-                x.copy_(x_h, non_blocking=True)
-                h2d += x_h.numel() * 2
+                used.append(x)
             update(dy_d, x, w, m, v)
+            done = torch.cuda.Event()
+            done.record(main)
+            for t in used:
+                last_use[t.data_ptr()] = done
         # the step's result: the device status word and one updated weight, read back to the host
         host_result[0:1].copy_(_lib.status_word(dev)[0:1].float(), non_blocking=True)
         host_result[1:2].copy_(params[-1][6][0, 0:1].float(), non_blocking=True)
+        join = torch.cuda.Event()
+        join.record(copy_stream)
+        main.wait_event(join)
         if sync:
-            torch.cuda.current_stream().synchronize()
+            main.synchronize()
         return h2d, 8
 
     def barrier():

@@ -84,7 +84,7 @@ def main():
     n_params = sum(p.numel() for p in model.parameters())
 
     if args.baseline:
-        opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01, fused=True)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01, fused=True, capturable=args.graph)
         manager, fused = None, 0
     else:
         from forge_b200 import FusedOptimizerManager, autograd
