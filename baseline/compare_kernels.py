@@ -126,6 +126,60 @@ def main():
         for k, vnote in notes.items():
             row[k + "_unavailable"] = vnote
         print(json.dumps(row), flush=True)
+        int8_row(name, V, H, dy, x, flush)
+
+
+def int8_row(name, V, H, dy, x, flush):
+    """int8 moments (codes + one fp32 scale per row and 64 columns): this library against the reference's
+    own Triton kernel (``kernel.py:1487-1539``) from identical state -- time, and agreement of W, codes
+    and scales after one step (the two sum the token axis in different orders, so a code may differ by
+    one where x / scale sits within fp32 noise of a rounding boundary)."""
+    dev = "cuda"
+    from forge_b200 import kernel as FK
+    row = {"shape": name, "V": V, "H": H, "BT": BT, "moments": "int8"}
+    bytes_ = (2 * 4 + 2 * 2 * 4 / 64) * V * H + 2 * BT * (V + H)
+    row["roofline_us"] = bytes_ / HBM * 1e6
+    try:
+        import fused_grad_optimizer.kernel as RK
+        assert "_ref" in RK.__file__, RK.__file__
+        arms = {"forge": FK.fused_grad_adamw_int8state, "ref-triton": RK.fused_grad_adamw_int8state}
+    except Exception as e:  # pragma: no cover
+        arms = {"forge": FK.fused_grad_adamw_int8state}
+        row["ref-triton_unavailable"] = f"{type(e).__name__}: {e}"
+
+    def fresh():
+        g = torch.Generator(device=dev).manual_seed(2)
+        w = (torch.randn(V, H, device=dev, generator=g) * 0.02).bfloat16()
+        mq = torch.randint(-127, 128, (V, H), device=dev, generator=g, dtype=torch.int8)
+        vq = torch.randint(0, 128, (V, H), device=dev, generator=g, dtype=torch.int8)
+        ms = torch.rand(V, H // 64, device=dev, generator=g) * 1e-5 + 1e-6
+        vs = torch.rand(V, H // 64, device=dev, generator=g) * 1e-9 + 1e-10
+        return w, mq, vq, ms, vs
+
+    outs = {}
+    for arm, fn in arms.items():
+        st = fresh()
+        try:
+            us = timeit(lambda s: fn(dy, x, *st, step=s, **HYPER), flush)
+            row[arm + "_us"] = round(us, 1)
+            row[arm + "_frac"] = round(row["roofline_us"] / us, 3)
+            st = fresh()
+            fn(dy, x, *st, step=5, **HYPER)
+            torch.cuda.synchronize()
+            outs[arm] = st
+        except Exception as e:  # pragma: no cover
+            row[arm + "_error"] = f"{type(e).__name__}: {str(e)[:160]}"
+            torch.cuda.synchronize()
+    if len(outs) == 2:
+        a, b = outs["forge"], outs["ref-triton"]
+        row["max_abs_dW"] = float((a[0].float() - b[0].float()).abs().max())
+        for nm, i in (("m", 1), ("v", 2)):
+            d = (a[i].int() - b[i].int()).abs()
+            row[nm + "_codes_equal_frac"] = float((d == 0).float().mean())
+            row[nm + "_codes_max_diff"] = int(d.max())
+        row["m_scale_max_rel"] = float(((a[3] - b[3]).abs() / b[3].abs()).max())
+        row["v_scale_max_rel"] = float(((a[4] - b[4]).abs() / b[4].abs()).max())
+    print(json.dumps(row), flush=True)
 
 
 if __name__ == "__main__":
