@@ -59,6 +59,13 @@ def workload_linears(name):
         return lin
     if name == "llama3.1-8b-layer":   # one decoder layer: the projection set of BASELINE configuration 1
         return [(n, V, H, g) for n, V, H, g in LAYER_LINEARS]
+    if name == "qwen3-32b-linears":   # BASELINE configuration 4: 64 layers, hidden 5120, 64/8 heads of 128, FFN 25600
+        hid, qd, kv, ffn, vocab = 5120, 8192, 1024, 25600, 151936
+        layer = [("q", qd, hid, "attn_in"), ("k", kv, hid, "attn_in"), ("v", kv, hid, "attn_in"), ("o", hid, qd, "attn_out"),
+                 ("gate", ffn, hid, "mlp_in"), ("up", ffn, hid, "mlp_in"), ("down", hid, ffn, "mlp_out")]
+        lin = [(f"l{i}.{n}", V, H, f"l{i}.{g}") for i in range(64) for n, V, H, g in layer]
+        lin.append(("lm_head", vocab, hid, "lm_head"))
+        return lin
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -204,9 +211,10 @@ def run_forge(args):
     for name, V, H, grp in linears:
         r0, r1 = row_range(V, rank, shard_world)
         w = torch.empty(r1 - r0, H, dtype=torch.bfloat16, device=dev).normal_(0.0, 0.02, generator=gen)
-        if args.moments == "int8":       # codes 0, scales 1: the reference's initial state (state.py:108-117)
-            m = (torch.zeros(r1 - r0, H, dtype=torch.int8, device=dev), torch.ones(r1 - r0, H // 64, device=dev))
-            v = (torch.zeros(r1 - r0, H, dtype=torch.int8, device=dev), torch.ones(r1 - r0, H // 64, device=dev))
+        if args.moments in ("int8", "fp8_block"):   # codes 0, scales 1: the reference's initial state (state.py:108-117)
+            code = torch.int8 if args.moments == "int8" else torch.float8_e4m3fn
+            m = (torch.zeros(r1 - r0, H, dtype=code, device=dev), torch.ones(r1 - r0, H // 64, device=dev))
+            v = (torch.zeros(r1 - r0, H, dtype=code, device=dev), torch.ones(r1 - r0, H // 64, device=dev))
         else:
             m = torch.zeros_like(w)
             v = torch.zeros_like(w)
@@ -215,6 +223,8 @@ def run_forge(args):
     def update(dy, x, w, m, v):
         if args.moments == "int8":
             K.fused_grad_adamw_int8state(dy, x, w, m[0], v[0], m[1], v[1], hyper_device=hyper_dev)
+        elif args.moments == "fp8_block":
+            K.fused_grad_adamw_fp8block(dy, x, w, m[0], v[0], m[1], v[1], hyper_device=hyper_dev)
         else:
             K.fused_grad_adamw(dy, x, w, m, v, hyper_device=hyper_dev)
 
@@ -461,7 +471,7 @@ def run_forge(args):
             "config": {"workload": args.workload, "bt": BT, "linears": launches, "weights": "bf16", "moments": args.moments,
                        "optimizer": "adamw", "launch": "cuda_graph" if g_dev is not None else "eager", "streams": n_streams,
                        "parallelism": (f"tp{world}-rows" + ("+gather-x" if do_gather else "")) if world > 1 else "single",
-                       "l2": "each weight and its moments are distinct buffers (45 GB in total), so every launch "
+                       "l2": f"each weight and its moments are distinct buffers ({peak_gb:.0f} GB in total), so every launch "
                              "streams state that is not in L2; no flush needed",
                        "parameters": sum(V * H for _, V, H, *_ in params)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -533,8 +543,8 @@ def main():
     ap.add_argument("--impl", default="forge", choices=["forge", "reference"])
     ap.add_argument("--workload", default="llama3.1-8b-linears")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--moments", default="bf16", choices=["bf16", "int8"],
-                    help="storage of the AdamW moments (int8: per-(row, 64 columns) absmax scales)")
+    ap.add_argument("--moments", default="bf16", choices=["bf16", "int8", "fp8_block"],
+                    help="storage of the AdamW moments (int8 / fp8_block: codes + one fp32 absmax scale per row and 64 columns)")
     ap.add_argument("--streams", type=int, default=4, help="streams the independent updates of a step are spread over")
     ap.add_argument("--gather-x", action="store_true",
                     help="N > 1: all-gather the feature-sharded X by NCCL inside the timed step")
