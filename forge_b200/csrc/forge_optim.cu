@@ -118,7 +118,13 @@ __global__ void __launch_bounds__(256) forge_optim_kernel(const OptimParams p) {
         load16<SES>(p.m, row * p.ld_state + col, m);
         load16<SES>(p.v, row * p.ld_state + col, v);
 #pragma unroll
-        for (int k = 0; k < 16; ++k) w[k] = adamw_update(w[k], g[k], m[k], v[k], hy);
+        for (int k = 0; k < 16; k += 2) {
+          float2 m2 = make_float2(m[k], m[k + 1]), v2 = make_float2(v[k], v[k + 1]);
+          const float2 w2 = adamw_update2(make_float2(w[k], w[k + 1]), make_float2(g[k], g[k + 1]), m2, v2, hy);
+          w[k] = w2.x; w[k + 1] = w2.y;
+          m[k] = m2.x; m[k + 1] = m2.y;
+          v[k] = v2.x; v[k + 1] = v2.y;
+        }
         store16<WES>(p.W, row * p.ld_w + col, w);
         store16<SES>(p.m, row * p.ld_state + col, m);
         store16<SES>(p.v, row * p.ld_state + col, v);
@@ -139,23 +145,37 @@ __global__ void __launch_bounds__(256) forge_optim_kernel(const OptimParams p) {
       }
       float m[16], v[16];
       float am = 0.0f, av = 0.0f;
+      if constexpr (ST == ST_INT8) {
 #pragma unroll
-      for (int k = 0; k < 16; ++k) {
-        const uint32_t mbits = (mq[k >> 2] >> (8 * (k & 3))) & 0xFFu;
-        const uint32_t vbits = (vq[k >> 2] >> (8 * (k & 3))) & 0xFFu;
+        for (int j = 0; j < 4; ++j) { mq[j] ^= 0x80808080u; vq[j] ^= 0x80808080u; }
+      }
+#pragma unroll
+      for (int k = 0; k < 16; k += 2) {
+        float2 m2, v2;
         if constexpr (ST == ST_INT8) {
-          m[k] = f_mul(static_cast<float>(static_cast<int>(static_cast<int8_t>(mbits))), sm_old);
-          v[k] = fmaxf(f_mul(static_cast<float>(static_cast<int>(static_cast<int8_t>(vbits))), sv_old), 1e-8f);
+          m2 = fmul2(int8x2_to_float(mq[k >> 2], k & 3), make_float2(sm_old, sm_old));
+          v2 = fmul2(int8x2_to_float(vq[k >> 2], k & 3), make_float2(sv_old, sv_old));
+          v2.x = fmaxf(v2.x, 1e-8f);
+          v2.y = fmaxf(v2.y, 1e-8f);
         } else if constexpr (ST == ST_FP8_BLOCK) {
-          m[k] = f_mul(e4m3_to_float(static_cast<uint8_t>(mbits)), sm_old);
-          v[k] = fmaxf(f_mul(e4m3_to_float(static_cast<uint8_t>(vbits)), sv_old), 1e-8f);
+          e4m3x2_to_float(mq[k >> 2] >> (8 * (k & 3)), m2.x, m2.y);
+          e4m3x2_to_float(vq[k >> 2] >> (8 * (k & 3)), v2.x, v2.y);
+          m2 = fmul2(m2, make_float2(sm_old, sm_old));
+          v2 = fmul2(v2, make_float2(sv_old, sv_old));
+          v2.x = fmaxf(v2.x, 1e-8f);
+          v2.y = fmaxf(v2.y, 1e-8f);
         } else {
-          m[k] = f_mul(e4m3_to_float(static_cast<uint8_t>(mbits)), s_m_t);
-          v[k] = f_mul(e5m2_to_float(static_cast<uint8_t>(vbits)), s_v_t);
+          e4m3x2_to_float(mq[k >> 2] >> (8 * (k & 3)), m2.x, m2.y);
+          e5m2x2_to_float(vq[k >> 2] >> (8 * (k & 3)), v2.x, v2.y);
+          m2 = fmul2(m2, make_float2(s_m_t, s_m_t));
+          v2 = fmul2(v2, make_float2(s_v_t, s_v_t));
         }
-        w[k] = adamw_update(w[k], g[k], m[k], v[k], hy);
-        am = fmaxf(am, fabsf(m[k]));
-        av = fmaxf(av, fabsf(v[k]));
+        const float2 w2 = adamw_update2(make_float2(w[k], w[k + 1]), make_float2(g[k], g[k + 1]), m2, v2, hy);
+        w[k] = w2.x; w[k + 1] = w2.y;
+        m[k] = m2.x; m[k + 1] = m2.y;
+        v[k] = v2.x; v[k + 1] = v2.y;
+        am = fmaxf(am, fmaxf(fabsf(m2.x), fabsf(m2.y)));
+        av = fmaxf(av, fmaxf(fabsf(v2.x), fabsf(v2.y)));
       }
       uint32_t mo[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
       if constexpr (ST == ST_INT8 || ST == ST_FP8_BLOCK) {
@@ -167,18 +187,22 @@ __global__ void __launch_bounds__(256) forge_optim_kernel(const OptimParams p) {
         const float sm_new = (ST == ST_INT8) ? int8_scale(am) : fp8blk_scale(am);
         const float sv_new = (ST == ST_INT8) ? int8_scale(av) : fp8blk_scale(av);
           const float rsm = f_div(1.0f, sm_new), rsv = f_div(1.0f, sv_new);
+        const float2 nsm2 = make_float2(-sm_new, -sm_new), nsv2 = make_float2(-sv_new, -sv_new);
+        const float2 rsm2 = make_float2(rsm, rsm), rsv2 = make_float2(rsv, rsv);
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          uint32_t mc, vc;
+        for (int j = 0; j < 4; ++j) {
+          const int k = 4 * j;
+          const float2 qm01 = div2_by_rcp(make_float2(m[k], m[k + 1]), nsm2, rsm2);
+          const float2 qm23 = div2_by_rcp(make_float2(m[k + 2], m[k + 3]), nsm2, rsm2);
+          const float2 qv01 = div2_by_rcp(make_float2(v[k], v[k + 1]), nsv2, rsv2);
+          const float2 qv23 = div2_by_rcp(make_float2(v[k + 2], v[k + 3]), nsv2, rsv2);
           if constexpr (ST == ST_INT8) {
-            mc = static_cast<uint32_t>(int8_code(m[k], sm_new, rsm)) & 0xFFu;
-            vc = static_cast<uint32_t>(int8_code(v[k], sv_new, rsv)) & 0xFFu;
+            mo[j] = int8x4_pack(int8x2_round(qm01), int8x2_round(qm23));
+            vo[j] = int8x4_pack(int8x2_round(qv01), int8x2_round(qv23));
           } else {
-            mc = e4m3_code(div_by_rcp(m[k], sm_new, rsm));
-            vc = e4m3_code(div_by_rcp(v[k], sv_new, rsv));
+            mo[j] = e4m3x2_code_bits(qm01.x, qm01.y) | (e4m3x2_code_bits(qm23.x, qm23.y) << 16);
+            vo[j] = e4m3x2_code_bits(qv01.x, qv01.y) | (e4m3x2_code_bits(qv23.x, qv23.y) << 16);
           }
-          mo[k >> 2] |= mc << (8 * (k & 3));
-          vo[k >> 2] |= vc << (8 * (k & 3));
         }
         if (live && (col % 64) == 0) {
           p.m_scale[row * p.ld_scale + col / 64] = sm_new;
@@ -188,9 +212,11 @@ __global__ void __launch_bounds__(256) forge_optim_kernel(const OptimParams p) {
         amax_m_t = fmaxf(amax_m_t, am);
         amax_v_t = fmaxf(amax_v_t, av);
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          mo[k >> 2] |= static_cast<uint32_t>(e4m3_code(f_mul(m[k], inv_m_t))) << (8 * (k & 3));
-          vo[k >> 2] |= static_cast<uint32_t>(e5m2_code(f_mul(v[k], inv_v_t))) << (8 * (k & 3));
+        for (int k = 0; k < 16; k += 2) {
+          const float2 mc = fmul2(make_float2(m[k], m[k + 1]), make_float2(inv_m_t, inv_m_t));
+          const float2 vc = fmul2(make_float2(v[k], v[k + 1]), make_float2(inv_v_t, inv_v_t));
+          mo[k >> 2] |= e4m3x2_code_bits(mc.x, mc.y) << (8 * (k & 3));
+          vo[k >> 2] |= e5m2x2_code_bits(vc.x, vc.y) << (8 * (k & 3));
         }
       }
       if (live) {
