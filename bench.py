@@ -335,26 +335,27 @@ def run_forge(args):
             h2d += src_h.numel() * 2
             return dst
 
+        # Linears of one group (q/k/v; gate/up) consume the same activation: X is uploaded once per
+        # group, into staging sets that alternate per group; every linear uploads its own dY.
+        n_grp, x_d = -1, None
         for i, (name, V, H, grp, r0, r1, w, m, v) in enumerate(params):
             slot = i & 1
             dy_d = upload(dys[r1 - r0], "dy", slot)
-            if do_gather:
-                new_grp = grp != last_grp
-                xs_d = upload(x_shard[H], "x", slot) if new_grp else None
-            else:
-                x = upload(x_full[H], "x", slot)
+            new_grp = grp != last_grp
+            if new_grp:
+                n_grp += 1
+                last_grp = grp
+                x_d = upload(x_shard[H] if do_gather else x_full[H], "x", n_grp & 1)
             ready = torch.cuda.Event()
             ready.record(copy_stream)
             main.wait_event(ready)
-            used = [dy_d]
+            used = [dy_d, x_d]
             if do_gather:
                 if new_grp:
-                    xg = all_gather_features(xs_d)
-                    used.append(xs_d)
-                    last_grp = grp
+                    xg = all_gather_features(x_d)
                 x = xg
             else:
-                used.append(x)
+                x = x_d
             update(dy_d, x, w, m, v)
             done = torch.cuda.Event()
             done.record(main)
