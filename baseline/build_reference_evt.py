@@ -13,7 +13,9 @@ import os
 import re
 import sys
 
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT")
+if not REF:
+    raise SystemExit("set REFERENCE_ROOT to the reference checkout")
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref", "evt")
 KEEP = ("128x128_1sm", "256x128_2sm_etile128x64", "256x256_2sm_etile128x64")

@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory from the REFERENCE's own code.
 
-Run once in a container that has the reference checkout (``REFERENCE_ROOT``, default
-``/root/reference``); the tests only read the ``.npz`` / ``.json`` files it writes, so nothing at test
+Run once in a container that has the reference checkout (its directory is taken from the
+``REFERENCE_ROOT`` environment variable); the tests only read the ``.npz`` / ``.json`` files it writes, so nothing at test
 time needs the reference.  Sources of truth, in order of strength:
 
 A. ``interp_*.npz`` -- the bodies of the reference's Triton kernels executed by Triton's CPU
@@ -32,7 +32,9 @@ import os
 import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT")
+if not REF:
+    raise SystemExit("set REFERENCE_ROOT to the reference checkout")
 sys.path.insert(0, os.path.join(REF, "src"))
 sys.path.insert(0, REF)
 
