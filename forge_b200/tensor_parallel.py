@@ -158,3 +158,82 @@ def gather_rows(shard: torch.Tensor, V: int, rank: int, world: int, group=None) 
     dist.all_gather_into_tensor(flat, padded, group=group)
     out = flat.view((world, tallest) + tuple(shard.shape[1:]))
     return torch.cat([out[r, : e - s] for r, (s, e) in enumerate(sizes)], dim=0)
+
+
+# ---------------------------------------------------------------------------------------------
+# Checkpoints of row shards.  Every row-indexed tensor (the weight, the moments or their codes, the
+# per-(row, block) scale arrays) is saved with the row range it covers, so a checkpoint written by R
+# ranks can be loaded by any other number of ranks: a rank assembles its rows from the overlapping
+# pieces.  The reference's state_dict (``state.py:179-205``) has neither shards nor fp8 state.
+# ---------------------------------------------------------------------------------------------
+_SCALAR_KEYS = ("optimizer_type", "step", "quantize_state", "state_mode")
+
+
+def shard_state_dict(layer: "RowShardedFusedLinear") -> dict:
+    """This rank's piece of a sharded checkpoint (tensors cloned to the CPU)."""
+    opt = layer.local.get_optimizer_state_dict()
+    if opt is not None:
+        opt = {k: (v.detach().cpu().clone() if torch.is_tensor(v) else v) for k, v in opt.items()}
+    return {"rows": (layer.row_start, layer.row_end), "out_features": layer.out_features,
+            "in_features": layer.in_features, "world": layer.world,
+            "weight": layer.local.weight.detach().cpu().clone(),
+            "bias": None if layer.local.bias is None else layer.local.bias.detach().cpu().clone(),
+            "optimizer": opt}
+
+
+def _rows_from_pieces(pieces, start: int, end: int) -> torch.Tensor:
+    """Rows [start, end) cut out of [(row0, row1, tensor with row1 - row0 rows), ...]."""
+    parts, at = [], start
+    for r0, r1, t in sorted(pieces, key=lambda p: p[0]):
+        lo, hi = max(r0, at), min(r1, end)
+        if lo < hi:
+            if lo != at:
+                raise ValueError(f"rows {at}..{lo} are missing from the checkpoint")
+            parts.append(t[lo - r0:hi - r0])
+            at = hi
+    if at != end:
+        raise ValueError(f"rows {at}..{end} are missing from the checkpoint")
+    return torch.cat(parts, dim=0) if len(parts) > 1 else parts[0].clone()
+
+
+def load_resharded(layer: "RowShardedFusedLinear", shards: list) -> None:
+    """Load this rank's rows from the pieces of a sharded checkpoint (``shard_state_dict`` of every
+    rank that wrote it, in any order, written with any world size)."""
+    if not shards:
+        raise ValueError("no shards given")
+    for s in shards:
+        if s["out_features"] != layer.out_features or s["in_features"] != layer.in_features:
+            raise ValueError("checkpoint belongs to a layer of another shape")
+    a, b = layer.row_start, layer.row_end
+    dev = layer.local.weight.device
+    with torch.no_grad():
+        w = _rows_from_pieces([(s["rows"][0], s["rows"][1], s["weight"]) for s in shards], a, b)
+        layer.local.weight.data.copy_(w.to(dev))
+        if layer.local.bias is not None and shards[0].get("bias") is not None:
+            bias = _rows_from_pieces([(s["rows"][0], s["rows"][1], s["bias"]) for s in shards], a, b)
+            layer.local.bias.data.copy_(bias.to(dev))
+    opts = [s["optimizer"] for s in shards]
+    if all(o is None for o in opts):
+        return
+    if any(o is None for o in opts):
+        raise ValueError("some shards carry optimizer state and some do not")
+    first = opts[0]
+    for o in opts[1:]:
+        for k in _SCALAR_KEYS:
+            if o.get(k) != first.get(k):
+                raise ValueError(f"shards disagree on {k!r}: {o.get(k)!r} vs {first.get(k)!r}")
+    merged = {k: first[k] for k in _SCALAR_KEYS if k in first}
+    for key, val in first.items():
+        if not torch.is_tensor(val):
+            continue
+        if val.dim() >= 2:      # row-indexed: moments, codes, per-(row, block) scales
+            merged[key] = _rows_from_pieces([(s["rows"][0], s["rows"][1], s["optimizer"][key]) for s in shards], a, b)
+        else:
+            # one scale per tensor (fp8 mode): the codes of a shard are relative to that shard's own
+            # scale, so they can only be taken over whole
+            exact = [s for s in shards if tuple(s["rows"]) == (a, b)]
+            if not exact:
+                raise ValueError("per-tensor fp8 state can only be loaded with the sharding it was saved with; "
+                                 "use state_mode='fp8_block' for checkpoints that must reshard")
+            merged[key] = exact[0]["optimizer"][key].clone()
+    layer.local.load_optimizer_state_dict(merged)

@@ -309,7 +309,8 @@ def test_fused_equals_unfused_twin_bitwise():
         assert torch.equal(a.view(torch.int16), b.view(torch.int16))
 
 
-@pytest.mark.parametrize("V,H", [(14336, 4096), (4096, 14336), (4096, 4096), (1024, 4096)])
+# the last shape has a single row tile: single-CTA units (no pairs), several rounds of them and a half-tile tail
+@pytest.mark.parametrize("V,H", [(14336, 4096), (4096, 14336), (4096, 4096), (1024, 4096), (128, 81920)])
 @pytest.mark.parametrize("mode", ["bf16", "int8"])
 def test_full_size_fused_equals_unfused_twin(V, H, mode):
     """The Llama-3.1-8B projection shapes at BT = 512 (many rounds of work units per SM pair, the
