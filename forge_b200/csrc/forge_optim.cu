@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(256) forge_optim_kernel(const OptimParams p) {
         av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 2));
         const float sm_new = (ST == ST_INT8) ? int8_scale(am) : fp8blk_scale(am);
         const float sv_new = (ST == ST_INT8) ? int8_scale(av) : fp8blk_scale(av);
-          const float rsm = f_div(1.0f, sm_new), rsv = f_div(1.0f, sv_new);
+          const float rsm = f_rcp(sm_new), rsv = f_rcp(sv_new);
         const float2 nsm2 = make_float2(-sm_new, -sm_new), nsv2 = make_float2(-sv_new, -sv_new);
         const float2 rsm2 = make_float2(rsm, rsm), rsv2 = make_float2(rsv, rsv);
 #pragma unroll

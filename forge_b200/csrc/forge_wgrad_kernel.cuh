@@ -838,7 +838,7 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           tmem_st_wait();
           const float sm_new = (ST == ST_INT8) ? int8_scale(am) : fp8blk_scale(am);
           const float sv_new = (ST == ST_INT8) ? int8_scale(av) : fp8blk_scale(av);
-          const float rsm = f_div(1.0f, sm_new), rsv = f_div(1.0f, sv_new);
+          const float rsm = f_rcp(sm_new), rsv = f_rcp(sv_new);
           const float2 nsm2 = make_float2(-sm_new, -sm_new), nsv2 = make_float2(-sv_new, -sv_new);
           const float2 rsm2 = make_float2(rsm, rsm), rsv2 = make_float2(rsv, rsv);
           uint32_t mcur[16];
