@@ -349,6 +349,41 @@ def test_full_size_fused_equals_unfused_twin(V, H, mode):
         assert torch.equal(ai, bi), f"{name}: {(ai != bi).sum().item()} of {ai.numel()} elements differ"
 
 
+def test_concurrent_streams_equal_sequential_bitwise():
+    """Several fused updates in flight at once on different streams (as in a multi-branch CUDA graph):
+    every SM is taken by one update at a time and the launches take over each other's SMs at their
+    ragged ends; each must produce the bits of a run on its own."""
+    BT = 256
+    shapes = [(1024, 4096), (4096, 1024), (2048, 2048), (136, 264), (4096, 4096), (1024, 1024)]
+    gen = torch.Generator(device=DEV).manual_seed(9)
+    jobs = []
+    for V, H in shapes:
+        dy = (torch.randn(BT, V, device=DEV, generator=gen) * 1e-2).bfloat16()
+        x = torch.randn(BT, H, device=DEV, generator=gen).bfloat16()
+        w = (torch.randn(V, H, device=DEV, generator=gen) * 0.02).bfloat16()
+        m = (torch.randn(V, H, device=DEV, generator=gen) * 1e-3).bfloat16()
+        v = (torch.randn(V, H, device=DEV, generator=gen).abs() * 1e-5).bfloat16()
+        jobs.append((dy, x, w, m, v))
+    ref = []
+    for dy, x, w, m, v in jobs:
+        st = (w.clone(), m.clone(), v.clone())
+        for step in range(1, 4):
+            K.fused_grad_adamw(dy, x, *st, **dict(ADAMW, step=step))
+        ref.append(st)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in range(4)]
+    got = [(w.clone(), m.clone(), v.clone()) for _, _, w, m, v in jobs]
+    torch.cuda.synchronize()
+    for step in range(1, 4):
+        for i, (dy, x, *_rest) in enumerate(jobs):
+            with torch.cuda.stream(streams[i % 4]):
+                K.fused_grad_adamw(dy, x, *got[i], **dict(ADAMW, step=step))
+    torch.cuda.synchronize()
+    for a, b in zip(ref, got):
+        for ta, tb in zip(a, b):
+            assert torch.equal(ta.view(torch.int16), tb.view(torch.int16))
+
+
 # ------------------------------------------------------------------ fp32 operands, edge cases, errors
 @pytest.mark.parametrize("BT,V,H", [(128, 256, 128), (64, 512, 256), (256, 1024, 512), (50, 136, 264)])
 def test_fp32_operands_close_to_fp32_oracle(BT, V, H):
