@@ -233,10 +233,10 @@ struct WgradCfg {
   static constexpr int kNMom = num_moments(OPT);
   static constexpr int kSES = state_elem_size(ST);
   static constexpr int kBK = OP_BK;
-  static constexpr int kNStage = (CG == 2) ? OP_STAGES + 2 : OP_STAGES;
+  static constexpr int kBaseStages = (CG == 2) ? OP_STAGES + 2 : OP_STAGES;
   static constexpr int kOpStageBytes = (TILE_M + TILE_N / CG) * kBK * 2;
   static constexpr int kCtrlBytes = 1024;
-  static constexpr int kRoom = SMEM_BUDGET - kCtrlBytes - 1024 - kNStage * kOpStageBytes;
+  static constexpr int kRoom = SMEM_BUDGET - kCtrlBytes - 1024 - kBaseStages * kOpStageBytes;
   // 64-column chunks when four such stages fit (always with one-byte codes, whose quantisation block
   // is 64 columns); otherwise 32-column chunks, which buy a deeper ring for the same bytes
   static constexpr int kCN = (kSES == 1 || 4 * state_stage_bytes(kWES, kSES, kNMom, 64) <= kRoom) ? 64 : 32;
@@ -249,6 +249,12 @@ struct WgradCfg {
   static constexpr int kNSS_raw = kRoom / kStageBytes;
   static constexpr int kNSS_cap = kNSS_raw >= 6 ? 6 : (kNSS_raw >= 4 ? 4 : 2);   // even, see the file comment
   static constexpr int kNSS = kNSS_cap > FORGE_MAX_STATE_STAGES ? FORGE_MAX_STATE_STAGES : kNSS_cap;
+  // Shared memory the state ring leaves over goes to operand stages (at most eight): with small
+  // states (plain SGD, one moment) the kernel is bound by the panel loads, whose rate is the bytes
+  // in flight over the L2 latency.
+  static constexpr int kSpare = kRoom - kNSS * kStageBytes;
+  static constexpr int kExtraStages = (kSpare / kOpStageBytes < 8 - kBaseStages) ? kSpare / kOpStageBytes : 8 - kBaseStages;
+  static constexpr int kNStage = kBaseStages + (kExtraStages > 0 ? kExtraStages : 0);
   static constexpr int kSmemBytes = kCtrlBytes + 1024 + kNStage * kOpStageBytes + kNSS * kStageBytes;
   static_assert(kNSS_raw >= 2, "two state stages must fit in shared memory");
   static_assert(kSES != 1 || kCN == 64, "one-byte codes need 64-column chunks (the quantisation block)");
