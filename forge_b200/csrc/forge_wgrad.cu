@@ -31,12 +31,16 @@ __global__ void split_f32_kernel(const float* __restrict__ src, int64_t rows, in
   }
 }
 
-// what the launcher needs to build the W / moment tensor maps for a given kernel configuration
+// what the launcher needs to build the tensor maps for a given kernel configuration
 struct StateTensors {
   void* W;
   void* m;
   void* v;
   int64_t V, H, ld_w, ld_state;
+  // bf16 operands as the kernel reads them (the split copies for fp32 inputs); bt = token rows
+  const void* dy;
+  const void* x;
+  int64_t bt, ld_dy, ld_x;
 };
 
 // Number of final tiles issued as 128-column halves when a weight has at least two rounds of
@@ -53,9 +57,18 @@ static int64_t tail_halves(int64_t tiles, int64_t workers) {
 }
 
 template <int W_DT, int ST, int OPT, int CG>
-static int launch_wgrad(const CUtensorMap& tm_dy, const CUtensorMap& tm_x, const StateTensors& t,
-                        WgradParams p, int sm_count, cudaStream_t stream) {
+static int launch_wgrad(const StateTensors& t, WgradParams p, int sm_count, cudaStream_t stream) {
   using Cfg = WgradCfg<W_DT, ST, OPT, CG>;
+  // operand panels: boxes of 64 columns x one pipeline stage of token rows, 128-byte swizzle
+  CUtensorMap tm_dy, tm_x;
+  memset(&tm_dy, 0, sizeof(tm_dy));
+  memset(&tm_x, 0, sizeof(tm_x));
+  p.num_kb = static_cast<int>((t.bt + Cfg::kBK - 1) / Cfg::kBK);
+  if (t.bt > 0) {
+    int rc0;
+    if ((rc0 = encode_tmap_2d(&tm_dy, t.dy, 2, true, t.bt, t.V, t.ld_dy, 64, Cfg::kBK, 128)) != FORGE_OK) return rc0;
+    if ((rc0 = encode_tmap_2d(&tm_x, t.x, 2, true, t.bt, t.H, t.ld_x, 64, Cfg::kBK, 128)) != FORGE_OK) return rc0;
+  }
   p.tiles_m = static_cast<int>((t.V + TILE_M * CG - 1) / (TILE_M * CG));
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   // One cluster per work unit; the hardware starts as many as fit (one CTA per SM) and the running
@@ -130,13 +143,12 @@ static bool pairs_enabled() {
 }
 
 template <int W_DT>
-static int dispatch_wgrad(int opt, int st, const CUtensorMap& a, const CUtensorMap& b, const StateTensors& t,
-                          const WgradParams& p, int sm_count, cudaStream_t s) {
+static int dispatch_wgrad(int opt, int st, const StateTensors& t, const WgradParams& p, int sm_count, cudaStream_t s) {
   const bool pair = pairs_enabled() && t.V > TILE_M && sm_count >= 2;
 #define FORGE_CASE(OPT_, ST_)                                                             \
   if (opt == OPT_ && st == ST_)                                                           \
-    return pair ? launch_wgrad<W_DT, ST_, OPT_, 2>(a, b, t, p, sm_count, s)               \
-                : launch_wgrad<W_DT, ST_, OPT_, 1>(a, b, t, p, sm_count, s);
+    return pair ? launch_wgrad<W_DT, ST_, OPT_, 2>(t, p, sm_count, s)                     \
+                : launch_wgrad<W_DT, ST_, OPT_, 1>(t, p, sm_count, s);
   FORGE_CASE(OPT_ADAMW, ST_BF16)
   FORGE_CASE(OPT_ADAMW, ST_F32)
   FORGE_CASE(OPT_ADAMW, ST_INT8)
@@ -226,23 +238,16 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
     dy = sa; x = sb; bt = 3 * bt_pad; ld_dy = a.V; ld_x = a.H;
   }
 
-  CUtensorMap tm_dy, tm_x;
-  int rc;
-  memset(&tm_dy, 0, sizeof(tm_dy));
-  memset(&tm_x, 0, sizeof(tm_x));
-  if (bt > 0) {
-    if ((rc = encode_tmap_2d(&tm_dy, dy, 2, true, bt, a.V, ld_dy, 64, OP_BK, 128)) != FORGE_OK) return rc;
-    if ((rc = encode_tmap_2d(&tm_x, x, 2, true, bt, a.H, ld_x, 64, OP_BK, 128)) != FORGE_OK) return rc;
-  }
   StateTensors t;
   t.W = a.W; t.m = a.state.m; t.v = a.state.v;
   t.V = a.V; t.H = a.H; t.ld_w = a.ld_w; t.ld_state = a.state.ld_state;
+  t.dy = dy; t.x = x; t.bt = bt; t.ld_dy = ld_dy; t.ld_x = ld_x;
 
   WgradParams p;
   p.BT = static_cast<int>(bt);
   p.V = static_cast<int>(a.V);
   p.H = static_cast<int>(a.H);
-  p.num_kb = static_cast<int>((bt + OP_BK - 1) / OP_BK);
+  p.num_kb = 0;   // set by the launcher (depends on the stage depth of the kernel configuration)
   p.tiles_m = 0;  // set by the launcher (depends on single CTAs vs CTA pairs)
   p.tiles_n = static_cast<int>((a.H + TILE_N - 1) / TILE_N);
   p.dy = static_cast<const uint8_t*>(dy);
@@ -257,8 +262,8 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
   p.v_absmax = a.state.v_absmax_next;
   p.status = a.status;
   p.hyper_dev = static_cast<const Hyper*>(a.hyper_device);
-  if (a.w_dtype == FORGE_DT_BF16) return dispatch_wgrad<DT_BF16>(opt, st, tm_dy, tm_x, t, p, di->sm_count, stream);
-  return dispatch_wgrad<DT_F32>(opt, st, tm_dy, tm_x, t, p, di->sm_count, stream);
+  if (a.w_dtype == FORGE_DT_BF16) return dispatch_wgrad<DT_BF16>(opt, st, t, p, di->sm_count, stream);
+  return dispatch_wgrad<DT_F32>(opt, st, t, p, di->sm_count, stream);
 }
 
 // ------------------------------------------------------------------------------------------------
