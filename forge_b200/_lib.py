@@ -109,6 +109,7 @@ class ForgeOptimArgs(ctypes.Structure):
 # every symbol include/forge_b200.h declares, with its ctypes signature
 _SIGNATURES = {
     "forge_wgrad_update": (ctypes.c_int, [ctypes.POINTER(ForgeWgradArgs), ctypes.c_void_p]),
+    "forge_wgrad_update_group": (ctypes.c_int, [ctypes.POINTER(ForgeWgradArgs), ctypes.c_int32, ctypes.c_void_p]),
     "forge_wgrad_update_static_scratch": (ctypes.c_int, [ctypes.POINTER(ForgeWgradArgs), ctypes.c_void_p]),
     "forge_hyper_pack": (ctypes.c_int, [ctypes.POINTER(ForgeHyper), ctypes.c_void_p]),
     "forge_wgrad_scratch_bytes": (ctypes.c_size_t, [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32]),
@@ -121,6 +122,7 @@ _SIGNATURES = {
          ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_int32)],
     ),
     "forge_read_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32), ctypes.c_void_p]),
+    "forge_selftest_wait_timeout": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p]),
     "forge_last_error_string": (ctypes.c_char_p, []),
     "forge_abi_version": (ctypes.c_int, []),
 }

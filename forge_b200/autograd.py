@@ -42,7 +42,10 @@ class FusedLinearFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, input, weight, bias, optimizer_state, optimizer_config, is_accumulating,
-                l2_manager, use_fused_backward=True):
+                l2_manager, use_fused_backward=True, update_group=None):
+        # update_group (no reference counterpart): a LayerUpdateGroup that collects the fused updates of
+        # several linears and issues them as one launch once every member has reported
+        ctx.update_group = update_group
         ctx.save_for_backward(input, weight, bias)
         ctx.optimizer_state = optimizer_state
         ctx.optimizer_config = optimizer_config
@@ -74,11 +77,46 @@ class FusedLinearFunction(torch.autograd.Function):
                 _apply_precomputed(total, weight, state, config)
             elif not ctx.use_fused_backward:
                 _apply_precomputed((dy2d.t() @ x2d).float(), weight, state, config)
+            elif ctx.update_group is not None:
+                ctx.update_group.add(weight, lambda: _apply_fused(dy2d, x2d, weight, state, config, ctx.l2_manager))
             else:
                 _apply_fused(dy2d, x2d, weight, state, config, ctx.l2_manager)
 
         grad_bias = dy2d.sum(0) if bias is not None else None
-        return grad_input, grad_weight, grad_bias, None, None, None, None, None
+        return grad_input, grad_weight, grad_bias, None, None, None, None, None, None
+
+
+class LayerUpdateGroup:
+    """The fused updates of a fixed set of linears (the projections of a decoder layer, or q / k / v)
+    issued as one launch.  Each member's backward records its update instead of launching it; when the
+    last member has reported, the group enqueues ``forge_wgrad_update_group`` on the current stream.
+    Deferring is safe because a weight is read by nothing between its own backward and the end of the
+    layer's backward: every dX GEMM of the members has been enqueued, on the same stream, before the
+    launch that rewrites the weights.  ``flush()`` issues whatever has been recorded (a member that
+    took no part in this backward pass would otherwise hold the others back);
+    ``FusedOptimizerManager.pre_step`` calls it.  No reference counterpart."""
+
+    def __init__(self, weights):
+        self._members = {w.data_ptr() for w in weights}
+        self._seen: set[int] = set()
+        self._group = K.UpdateGroup()
+
+    def __len__(self):
+        return len(self._members)
+
+    def add(self, weight, launch):
+        wid = weight.data_ptr()
+        if wid in self._seen:          # the same linear twice in one pass: issue what is there first
+            self.flush()
+        with self._group.record():
+            launch()
+        self._seen.add(wid)
+        if self._seen >= self._members:
+            self.flush()
+
+    def flush(self):
+        self._seen.clear()
+        self._group.flush()
 
 
 def _begin_update(state, config):

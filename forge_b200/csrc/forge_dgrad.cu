@@ -10,6 +10,7 @@
 // Four 128 x 128 fp32 accumulators live in tensor memory, so the MMAs of the next tile start while
 // the previous tile is still being written out.
 #include <algorithm>
+#include <atomic>
 
 #include "forge_host.h"
 #include "forge_ptx.cuh"
@@ -187,6 +188,9 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   }
 
 done:
+  // the single-lane roles leave their loops alone; bring every warp back together before the
+  // CTA-wide barrier (an aligned barrier executed by a diverged warp is undefined)
+  __syncwarp();
   tc_fence_before();
   __syncthreads();
   if (*abort_word != 0) {
@@ -234,13 +238,13 @@ extern "C" int forge_dgrad(const void* dY, const void* W, void* dX, int64_t BT, 
   p.tiles_n = static_cast<int>((H + BN - 1) / BN);
   p.num_kb = static_cast<int>((V + BK - 1) / BK);
   p.status = status;
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];   // per device: the shared-memory opt-in has been made
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+  if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(forge_dgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   const int grid = static_cast<int>(std::min<int64_t>(tiles, di->sm_count));

@@ -81,14 +81,14 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Bounded wait.  `abort_word` lives in shared memory; a non-zero value means some thread of the
 // CTA already gave up.  Returns false when the wait was abandoned.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word,
-                                          int code) {
+                                          int code, uint64_t limit_ns = FORGE_WAIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 0u) {
       if (*abort_word != 0) return false;
-      if (global_timer_ns() - t0 > FORGE_WAIT_NS) break;
+      if (global_timer_ns() - t0 > limit_ns) break;
     }
   }
   atomicCAS(const_cast<int*>(abort_word), 0, code);

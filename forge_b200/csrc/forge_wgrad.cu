@@ -3,6 +3,9 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
+#include <mutex>
+#include <vector>
 
 #include "forge_host.h"
 #include "forge_wgrad_kernel.cuh"
@@ -31,8 +34,9 @@ __global__ void split_f32_kernel(const float* __restrict__ src, int64_t rows, in
   }
 }
 
-// what the launcher needs to build the tensor maps for a given kernel configuration
-struct StateTensors {
+// One validated problem of a launch: what the launcher needs to build the tensor maps and the
+// kernel's per-problem parameters for whichever kernel configuration is chosen.
+struct Prepared {
   void* W;
   void* m;
   void* v;
@@ -41,9 +45,18 @@ struct StateTensors {
   const void* dy;
   const void* x;
   int64_t bt, ld_dy, ld_x;
+  float* m_scale;
+  float* v_scale;
+  int64_t ld_scale;
+  float* m_absmax;
+  float* v_absmax;
+  Hyper hyper;
+  const Hyper* hyper_dev;
+  int32_t* status;
+  int w_dtype, opt, st;
 };
 
-// Number of final tiles issued as 128-column halves when a weight has at least two rounds of
+// Number of final tiles issued as 128-column halves when a launch has at least two rounds of
 // tiles: by default one half per worker (measured on 14336 x 4096 and 4096 x 4096: 1.5 % and 3.7 %
 // faster than whole tiles to the end; more halves were slower).  FORGE_TAIL_HALVES=<n> in the
 // environment (a tuning aid, read once) overrides it.
@@ -56,63 +69,99 @@ static int64_t tail_halves(int64_t tiles, int64_t workers) {
   return tiles >= 2 * workers ? workers / 2 : 0;
 }
 
+// one launch for `n` problems (1 <= n <= MAX_GROUP) of one kernel configuration
 template <int W_DT, int ST, int OPT, int CG>
-static int launch_wgrad(const StateTensors& t, WgradParams p, int sm_count, cudaStream_t stream) {
+static int launch_wgrad(const Prepared* items, int n, int sm_count, cudaStream_t stream) {
   using Cfg = WgradCfg<W_DT, ST, OPT, CG>;
-  // operand panels: boxes of 64 columns x one pipeline stage of token rows, 128-byte swizzle
-  CUtensorMap tm_dy, tm_x;
-  memset(&tm_dy, 0, sizeof(tm_dy));
-  memset(&tm_x, 0, sizeof(tm_x));
-  p.num_kb = static_cast<int>((t.bt + Cfg::kBK - 1) / Cfg::kBK);
-  if (t.bt > 0) {
-    int rc0;
-    if ((rc0 = encode_tmap_2d(&tm_dy, t.dy, 2, true, t.bt, t.V, t.ld_dy, 64, Cfg::kBK, 128)) != FORGE_OK) return rc0;
-    if ((rc0 = encode_tmap_2d(&tm_x, t.x, 2, true, t.bt, t.H, t.ld_x, 64, Cfg::kBK, 128)) != FORGE_OK) return rc0;
-  }
-  p.tiles_m = static_cast<int>((t.V + TILE_M * CG - 1) / (TILE_M * CG));
-  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
-  // One cluster per work unit; the hardware starts as many as fit (one CTA per SM) and the running
-  // ones take over the units of the rest.  A weight whose tiles would leave half of the SMs idle is
-  // cut into 128-column halves; otherwise the last `tail` tiles are, to shorten the ragged end.
-  const int64_t workers = sm_count / CG;
-  const int64_t tail = std::min<int64_t>(tiles, tail_halves(tiles, workers));
-  const int64_t split_from = (2 * tiles <= workers) ? 0 : tiles - tail;
-  const int64_t units = split_from + 2 * (tiles - split_from);
-  if (units * CG > 0x7fffffffLL) return fail(FORGE_ERR_SHAPE, "weight of %lld x %lld is too large", (long long)t.V, (long long)t.H);
-  p.split_from = static_cast<int>(split_from);
-  p.num_units = static_cast<int>(units);
-  const int grid = CG * p.num_units;
-  // boxes of 128 rows x one swizzle row of a chunk; the same maps serve the loads and the stores
-  CUtensorMap tm_w, tm_m, tm_v;
-  int rc;
   using WG = BoxGeom<Cfg::kWRB>;
-  if ((rc = encode_tmap_2d(&tm_w, t.W, Cfg::kWES, true, t.V, t.H, t.ld_w, WG::kBoxRowBytes / Cfg::kWES, 128,
-                           WG::kSwizzle)) != FORGE_OK)
-    return rc;
-  tm_m = tm_w;
-  tm_v = tm_w;
-  if constexpr (Cfg::kNMom > 0) {
-    using SG = BoxGeom<Cfg::kSRB>;
-    if ((rc = encode_tmap_2d(&tm_m, t.m, Cfg::kSES, Cfg::kSES != 1, t.V, t.H, t.ld_state,
-                             SG::kBoxRowBytes / Cfg::kSES, 128, SG::kSwizzle)) != FORGE_OK)
+  WgradGroup g;   // the kernel's parameter block (several kilobytes, passed by value)
+  g.n = n;
+  g.status = nullptr;
+  int64_t total_tiles = 0;
+  for (int i = 0; i < n; ++i) {
+    const Prepared& t = items[i];
+    WgradProblem& q = g.prob[i];
+    if (g.status == nullptr) g.status = t.status;
+    q.BT = static_cast<int>(t.bt);
+    q.V = static_cast<int>(t.V);
+    q.H = static_cast<int>(t.H);
+    q.num_kb = static_cast<int>((t.bt + Cfg::kBK - 1) / Cfg::kBK);
+    q.tiles_m = static_cast<int>((t.V + TILE_M * CG - 1) / (TILE_M * CG));
+    q.tiles_n = static_cast<int>((t.H + TILE_N - 1) / TILE_N);
+    q.ld_scale = static_cast<int>(t.ld_scale);
+    q.dy = static_cast<const uint8_t*>(t.dy);
+    q.x = static_cast<const uint8_t*>(t.x);
+    q.ld_dy_bytes = t.ld_dy * 2;
+    q.ld_x_bytes = t.ld_x * 2;
+    q.m_scale = t.m_scale;
+    q.v_scale = t.v_scale;
+    q.m_absmax = t.m_absmax;
+    q.v_absmax = t.v_absmax;
+    q.hyper_dev = t.hyper_dev;
+    q.hyper = t.hyper;
+    total_tiles += static_cast<int64_t>(q.tiles_m) * q.tiles_n;
+    int rc;
+    // boxes of 128 rows x one swizzle row of a chunk; the same maps serve the loads and the stores
+    if ((rc = encode_tmap_2d(&q.tm_w, t.W, Cfg::kWES, true, t.V, t.H, t.ld_w, WG::kBoxRowBytes / Cfg::kWES, 128,
+                             WG::kSwizzle)) != FORGE_OK)
       return rc;
-    if constexpr (Cfg::kNMom > 1) {
-      if ((rc = encode_tmap_2d(&tm_v, t.v, Cfg::kSES, Cfg::kSES != 1, t.V, t.H, t.ld_state,
+    q.tm_m = q.tm_w;
+    q.tm_v = q.tm_w;
+    if constexpr (Cfg::kNMom > 0) {
+      using SG = BoxGeom<Cfg::kSRB>;
+      if ((rc = encode_tmap_2d(&q.tm_m, t.m, Cfg::kSES, Cfg::kSES != 1, t.V, t.H, t.ld_state,
                                SG::kBoxRowBytes / Cfg::kSES, 128, SG::kSwizzle)) != FORGE_OK)
         return rc;
+      if constexpr (Cfg::kNMom > 1) {
+        if ((rc = encode_tmap_2d(&q.tm_v, t.v, Cfg::kSES, Cfg::kSES != 1, t.V, t.H, t.ld_state,
+                                 SG::kBoxRowBytes / Cfg::kSES, 128, SG::kSwizzle)) != FORGE_OK)
+          return rc;
+      }
+    }
+    // operand panels: boxes of 64 columns x one pipeline stage of token rows, 128-byte swizzle; with no
+    // tokens the operand maps are never used, valid ones are passed anyway
+    q.tm_dy = q.tm_w;
+    q.tm_x = q.tm_w;
+    if (t.bt > 0) {
+      if ((rc = encode_tmap_2d(&q.tm_dy, t.dy, 2, true, t.bt, t.V, t.ld_dy, 64, Cfg::kBK, 128)) != FORGE_OK) return rc;
+      if ((rc = encode_tmap_2d(&q.tm_x, t.x, 2, true, t.bt, t.H, t.ld_x, 64, Cfg::kBK, 128)) != FORGE_OK) return rc;
     }
   }
+  // One cluster per work unit; the hardware starts as many as fit (one CTA per SM) and the running
+  // ones take over the units of the rest.  The units of the problems follow each other in the order
+  // the problems were given.  A launch whose tiles would leave half of the SMs idle is cut into
+  // 128-column halves throughout; otherwise the last `tail` tiles of the launch are, to shorten the
+  // ragged end.
+  const int64_t workers = sm_count / CG;
+  int64_t halves = (2 * total_tiles <= workers) ? total_tiles : std::min<int64_t>(total_tiles, tail_halves(total_tiles, workers));
+  int64_t units = 0;
+  for (int i = n - 1; i >= 0; --i) {
+    WgradProblem& q = g.prob[i];
+    const int64_t tiles = static_cast<int64_t>(q.tiles_m) * q.tiles_n;
+    const int64_t h = std::min<int64_t>(tiles, halves);
+    halves -= h;
+    q.split_from = static_cast<int>(tiles - h);
+    q.num_units = static_cast<int>(tiles + h);
+    units += tiles + h;
+  }
+  if (units * CG > 0x7fffffffLL) return fail(FORGE_ERR_SHAPE, "launch of %lld work units is too large", (long long)units);
+  int base = 0;
+  for (int i = 0; i < n; ++i) {
+    g.prob[i].unit_base = base;
+    base += g.prob[i].num_units;
+  }
+  g.num_units = base;
+  const int grid = CG * g.num_units;
   auto kern = forge_wgrad_kernel<W_DT, ST, OPT, CG>;
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];   // per device: the shared-memory opt-in of this configuration has been made
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+  if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess)
       return fail(FORGE_ERR_CUDA, "cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
-  // with no tokens the operand maps are never used; pass valid ones anyway
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
@@ -125,15 +174,14 @@ static int launch_wgrad(const StateTensors& t, WgradParams p, int sm_count, cuda
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p.num_kb > 0 ? tm_dy : tm_w, p.num_kb > 0 ? tm_x : tm_w, tm_w, tm_m,
-                                     tm_v, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, g);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "wgrad kernel launch: %s", cudaGetErrorString(e));
   return FORGE_OK;
 }
 
-// CTA pairs are used whenever the weight has more than one 128-row tile; FORGE_CTA_PAIRS=0 in the
-// environment keeps single CTAs (a tuning / bisecting aid, read once).
+// CTA pairs are used whenever a weight of the launch has more than one 128-row tile;
+// FORGE_CTA_PAIRS=0 in the environment keeps single CTAs (a tuning / bisecting aid, read once).
 static bool pairs_enabled() {
   static const bool on = [] {
     const char* e = getenv("FORGE_CTA_PAIRS");
@@ -143,12 +191,15 @@ static bool pairs_enabled() {
 }
 
 template <int W_DT>
-static int dispatch_wgrad(int opt, int st, const StateTensors& t, const WgradParams& p, int sm_count, cudaStream_t s) {
-  const bool pair = pairs_enabled() && t.V > TILE_M && sm_count >= 2;
+static int dispatch_wgrad(const Prepared* items, int n, int sm_count, cudaStream_t s) {
+  const int opt = items[0].opt, st = items[0].st;
+  bool pair = false;
+  for (int i = 0; i < n; ++i) pair = pair || items[i].V > TILE_M;
+  pair = pair && pairs_enabled() && sm_count >= 2;
 #define FORGE_CASE(OPT_, ST_)                                                             \
   if (opt == OPT_ && st == ST_)                                                           \
-    return pair ? launch_wgrad<W_DT, ST_, OPT_, 2>(t, p, sm_count, s)                     \
-                : launch_wgrad<W_DT, ST_, OPT_, 1>(t, p, sm_count, s);
+    return pair ? launch_wgrad<W_DT, ST_, OPT_, 2>(items, n, sm_count, s)                 \
+                : launch_wgrad<W_DT, ST_, OPT_, 1>(items, n, sm_count, s);
   FORGE_CASE(OPT_ADAMW, ST_BF16)
   FORGE_CASE(OPT_ADAMW, ST_F32)
   FORGE_CASE(OPT_ADAMW, ST_INT8)
@@ -163,22 +214,12 @@ static int dispatch_wgrad(int opt, int st, const StateTensors& t, const WgradPar
   return fail(FORGE_ERR_UNSUPPORTED, "optimizer %d with state mode %d is not built", opt, st);
 }
 
-}  // namespace forge
-
-using namespace forge;
-
-extern "C" size_t forge_wgrad_scratch_bytes(int64_t BT, int64_t V, int64_t H, int32_t operand_dtype) {
-  if (operand_dtype != FORGE_DT_F32 || BT <= 0 || V <= 0 || H <= 0) return 0;
-  const int64_t bt_pad = (BT + 63) / 64 * 64;
-  return static_cast<size_t>(3 * bt_pad) * static_cast<size_t>(V + H) * sizeof(__nv_bfloat16);
-}
-
-extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream) {
-  if (args == nullptr) return fail(FORGE_ERR_INVALID_ARG, "forge_wgrad_update: args is NULL");
-  const ForgeWgradArgs& a = *args;
-  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+// Checks one argument block and fills `out`.  Launches nothing.  `*skip` is set for an empty
+// parameter (V or H zero), which needs no work.
+static int prepare(const ForgeWgradArgs& a, Prepared* out, bool* skip) {
+  *skip = false;
   if (a.BT < 0 || a.V < 0 || a.H < 0) return fail(FORGE_ERR_INVALID_ARG, "negative dimension");
-  if (a.V == 0 || a.H == 0) return FORGE_OK;  // empty parameter: nothing to update
+  if (a.V == 0 || a.H == 0) { *skip = true; return FORGE_OK; }  // empty parameter: nothing to update
   if (a.W == nullptr) return fail(FORGE_ERR_INVALID_ARG, "W is NULL");
   if (a.BT > 0 && (a.dY == nullptr || a.X == nullptr)) return fail(FORGE_ERR_INVALID_ARG, "dY or X is NULL");
   if (a.BT > (1 << 28) || a.V > (1ll << 30) || a.H > (1ll << 30)) return fail(FORGE_ERR_SHAPE, "dimension too large");
@@ -195,11 +236,6 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
     return fail(FORGE_ERR_INVALID_ARG, "step must be >= 1 (got %d)", a.hyper.step);
   if (a.hyper_device != nullptr && (reinterpret_cast<uintptr_t>(a.hyper_device) & 15u) != 0)
     return fail(FORGE_ERR_ALIGNMENT, "hyper_device is not 16-byte aligned");
-
-  const DeviceInfo* di = current_device_info();
-  if (di == nullptr) return FORGE_ERR_CUDA;
-  if (di->cc_major != 10) return fail(FORGE_ERR_DEVICE, "device has compute capability %d.%d; sm_100 is required", di->cc_major, di->cc_minor);
-
   const int nm = num_moments(opt);
   if (nm > 0 && a.state.m == nullptr) return fail(FORGE_ERR_INVALID_ARG, "first moment buffer is NULL");
   if (nm > 1 && a.state.v == nullptr) return fail(FORGE_ERR_INVALID_ARG, "second moment buffer is NULL");
@@ -215,55 +251,104 @@ extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream)
         a.state.v_absmax_next == nullptr)
       return fail(FORGE_ERR_INVALID_ARG, "fp8 per-tensor scale / absmax pointers are NULL");
   }
-
-  // operands: bf16 directly, fp32 through the split into scratch
-  const void* dy = a.dY;
-  const void* x = a.X;
-  int64_t bt = a.BT, ld_dy = a.ld_dy, ld_x = a.ld_x;
   if (a.BT > 0 && a.operand_dtype == FORGE_DT_F32) {
     const size_t need = forge_wgrad_scratch_bytes(a.BT, a.V, a.H, FORGE_DT_F32);
     if (a.scratch == nullptr || a.scratch_bytes < need)
       return fail(FORGE_ERR_SCRATCH, "fp32 operands need %zu bytes of scratch (got %zu)", need, a.scratch_bytes);
     if (!aligned16(a.scratch)) return fail(FORGE_ERR_ALIGNMENT, "scratch is not 16-byte aligned");
-    const int64_t bt_pad = (a.BT + 63) / 64 * 64;
-    __nv_bfloat16* sa = static_cast<__nv_bfloat16*>(a.scratch);
-    __nv_bfloat16* sb = sa + 3 * bt_pad * a.V;
-    const int threads = 256;
-    const int blocks_a = static_cast<int>(std::min<int64_t>((bt_pad * a.V + threads - 1) / threads, 148 * 8));
-    const int blocks_b = static_cast<int>(std::min<int64_t>((bt_pad * a.H + threads - 1) / threads, 148 * 8));
-    split_f32_kernel<<<blocks_a, threads, 0, stream>>>(static_cast<const float*>(a.dY), a.BT, a.V, a.ld_dy, bt_pad, sa, 0);
-    split_f32_kernel<<<blocks_b, threads, 0, stream>>>(static_cast<const float*>(a.X), a.BT, a.H, a.ld_x, bt_pad, sb, 1);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "operand split launch: %s", cudaGetErrorString(e));
-    dy = sa; x = sb; bt = 3 * bt_pad; ld_dy = a.V; ld_x = a.H;
   }
-
-  StateTensors t;
+  Prepared& t = *out;
   t.W = a.W; t.m = a.state.m; t.v = a.state.v;
   t.V = a.V; t.H = a.H; t.ld_w = a.ld_w; t.ld_state = a.state.ld_state;
-  t.dy = dy; t.x = x; t.bt = bt; t.ld_dy = ld_dy; t.ld_x = ld_x;
+  t.dy = a.dY; t.x = a.X; t.bt = a.BT; t.ld_dy = a.ld_dy; t.ld_x = a.ld_x;
+  t.m_scale = a.state.m_scale;
+  t.v_scale = a.state.v_scale;
+  t.ld_scale = a.state.ld_scale;
+  t.m_absmax = a.state.m_absmax_next;
+  t.v_absmax = a.state.v_absmax_next;
+  t.hyper = make_hyper(a.hyper);
+  t.hyper_dev = static_cast<const Hyper*>(a.hyper_device);
+  t.status = a.status;
+  t.w_dtype = a.w_dtype; t.opt = opt; t.st = st;
+  return FORGE_OK;
+}
 
-  WgradParams p;
-  p.BT = static_cast<int>(bt);
-  p.V = static_cast<int>(a.V);
-  p.H = static_cast<int>(a.H);
-  p.num_kb = 0;   // set by the launcher (depends on the stage depth of the kernel configuration)
-  p.tiles_m = 0;  // set by the launcher (depends on single CTAs vs CTA pairs)
-  p.tiles_n = static_cast<int>((a.H + TILE_N - 1) / TILE_N);
-  p.dy = static_cast<const uint8_t*>(dy);
-  p.x = static_cast<const uint8_t*>(x);
-  p.ld_dy_bytes = ld_dy * 2;
-  p.ld_x_bytes = ld_x * 2;
-  p.hyper = make_hyper(a.hyper);
-  p.m_scale = a.state.m_scale;
-  p.v_scale = a.state.v_scale;
-  p.ld_scale = static_cast<int>(a.state.ld_scale);
-  p.m_absmax = a.state.m_absmax_next;
-  p.v_absmax = a.state.v_absmax_next;
-  p.status = a.status;
-  p.hyper_dev = static_cast<const Hyper*>(a.hyper_device);
-  if (a.w_dtype == FORGE_DT_BF16) return dispatch_wgrad<DT_BF16>(opt, st, t, p, di->sm_count, stream);
-  return dispatch_wgrad<DT_F32>(opt, st, t, p, di->sm_count, stream);
+// fp32 operands: split into bf16 hi / lo parts in the caller's scratch (see split_f32_kernel) and
+// point the problem at the stacked copies
+static int split_operands(const ForgeWgradArgs& a, Prepared* t, cudaStream_t stream) {
+  const int64_t bt_pad = (a.BT + 63) / 64 * 64;
+  __nv_bfloat16* sa = static_cast<__nv_bfloat16*>(a.scratch);
+  __nv_bfloat16* sb = sa + 3 * bt_pad * a.V;
+  const int threads = 256;
+  const int blocks_a = static_cast<int>(std::min<int64_t>((bt_pad * a.V + threads - 1) / threads, 148 * 8));
+  const int blocks_b = static_cast<int>(std::min<int64_t>((bt_pad * a.H + threads - 1) / threads, 148 * 8));
+  split_f32_kernel<<<blocks_a, threads, 0, stream>>>(static_cast<const float*>(a.dY), a.BT, a.V, a.ld_dy, bt_pad, sa, 0);
+  split_f32_kernel<<<blocks_b, threads, 0, stream>>>(static_cast<const float*>(a.X), a.BT, a.H, a.ld_x, bt_pad, sb, 1);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "operand split launch: %s", cudaGetErrorString(e));
+  t->dy = sa; t->x = sb; t->bt = 3 * bt_pad; t->ld_dy = a.V; t->ld_x = a.H;
+  return FORGE_OK;
+}
+
+}  // namespace forge
+
+using namespace forge;
+
+extern "C" size_t forge_wgrad_scratch_bytes(int64_t BT, int64_t V, int64_t H, int32_t operand_dtype) {
+  if (operand_dtype != FORGE_DT_F32 || BT <= 0 || V <= 0 || H <= 0) return 0;
+  const int64_t bt_pad = (BT + 63) / 64 * 64;
+  return static_cast<size_t>(3 * bt_pad) * static_cast<size_t>(V + H) * sizeof(__nv_bfloat16);
+}
+
+extern "C" int forge_wgrad_update_group(const ForgeWgradArgs* args, int32_t count, void* cuda_stream) {
+  if (count < 0) return fail(FORGE_ERR_INVALID_ARG, "forge_wgrad_update_group: negative count");
+  if (count == 0) return FORGE_OK;
+  if (args == nullptr) return fail(FORGE_ERR_INVALID_ARG, "forge_wgrad_update_group: args is NULL");
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // every block is checked before anything is launched: a bad entry leaves all weights untouched
+  std::vector<Prepared> items;
+  std::vector<int> source;
+  items.reserve(count);
+  source.reserve(count);
+  for (int32_t i = 0; i < count; ++i) {
+    Prepared t;
+    bool skip = false;
+    const int rc = prepare(args[i], &t, &skip);
+    if (rc != FORGE_OK) return rc;
+    if (skip) continue;
+    items.push_back(t);
+    source.push_back(i);
+  }
+  if (items.empty()) return FORGE_OK;
+  const DeviceInfo* di = current_device_info();
+  if (di == nullptr) return FORGE_ERR_CUDA;
+  if (di->cc_major != 10) return fail(FORGE_ERR_DEVICE, "device has compute capability %d.%d; sm_100 is required", di->cc_major, di->cc_minor);
+  for (size_t k = 0; k < items.size(); ++k) {
+    const ForgeWgradArgs& a = args[source[k]];
+    if (a.BT > 0 && a.operand_dtype == FORGE_DT_F32) {
+      const int rc = split_operands(a, &items[k], stream);
+      if (rc != FORGE_OK) return rc;
+    }
+  }
+  // consecutive entries of one kernel configuration share a launch, MAX_GROUP at most
+  size_t k = 0;
+  while (k < items.size()) {
+    size_t e = k + 1;
+    while (e < items.size() && e - k < static_cast<size_t>(MAX_GROUP) && items[e].w_dtype == items[k].w_dtype &&
+           items[e].opt == items[k].opt && items[e].st == items[k].st)
+      ++e;
+    const int n = static_cast<int>(e - k);
+    const int rc = (items[k].w_dtype == FORGE_DT_BF16) ? dispatch_wgrad<DT_BF16>(&items[k], n, di->sm_count, stream)
+                                                       : dispatch_wgrad<DT_F32>(&items[k], n, di->sm_count, stream);
+    if (rc != FORGE_OK) return rc;
+    k = e;
+  }
+  return FORGE_OK;
+}
+
+extern "C" int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream) {
+  if (args == nullptr) return fail(FORGE_ERR_INVALID_ARG, "forge_wgrad_update: args is NULL");
+  return forge_wgrad_update_group(args, 1, cuda_stream);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -284,12 +369,14 @@ static __device__ __align__(256) unsigned char g_static_scratch[FORGE_STATIC_SCR
 // the address a kernel can use comes from cudaGetSymbolAddress, asked once per device (and once per
 // calling thread, which also makes sure that thread has the device's context bound).
 static int static_scratch_address(void** out) {
-  static void* cached[64] = {};
+  static void* cached[64] = {};            // guarded by cache_mutex
+  static std::mutex cache_mutex;
   static thread_local bool thread_ready[64] = {};
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= 64)
     return fail(FORGE_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(cache_mutex);
   if (cached[dev] == nullptr || !thread_ready[dev]) {
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_static_scratch);

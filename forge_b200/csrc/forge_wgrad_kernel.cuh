@@ -3,9 +3,14 @@
 //   dW[v,h] = sum_bt dY[bt,v] * X[bt,h]          (bf16 x bf16, fp32 accumulate in tensor memory)
 //   (W, moments)[v,h] <- optimizer(W, moments, dW)   applied to the accumulator tile on chip
 //
-// No gradient tensor is written to global memory.  This replaces, for one launch per linear, the
-// reference's fused kernels (src/fused_grad_optimizer/kernel.py:212-317 AdamW, :122-205 SGD,
-// :324-478 int8 moments, kernel_fp8_state.py:204-295 fp8 moments).
+// No gradient tensor is written to global memory.  This replaces the reference's fused kernels
+// (src/fused_grad_optimizer/kernel.py:212-317 AdamW, :122-205 SGD, :324-478 int8 moments,
+// kernel_fp8_state.py:204-295 fp8 moments).  The reference launches one kernel per linear; one launch
+// here updates a GROUP of up to MAX_GROUP weights of the same kernel configuration (say the q / k / v
+// projections, or all seven projections of a decoder layer): the work units of the problems are
+// numbered one after the other, the roles look up the problem a unit belongs to, and the pipelines
+// (operand ring, state ring, accumulators) run on across problem boundaries, so the start-up and the
+// ragged end of a launch are paid once per group instead of once per weight.
 //
 // Structure: one persistent CTA per SM, 12 warps.
 //   warp 0      TMA producer of the dY / X panels (both operands are M/N-major in memory: dY is
@@ -199,24 +204,37 @@ __device__ __forceinline__ void st16_bytes(uint8_t* buf, int r, int g, const uin
 }
 
 // kernel parameters ------------------------------------------------------------------------------
-struct WgradParams {
+constexpr int MAX_GROUP = 8;   // weights per launch
+
+// One weight of a launch.  The tensor maps live in the kernel's parameter space; a role passes the
+// address of the map of the problem it is working on to the copy engine.
+struct alignas(64) WgradProblem {
+  CUtensorMap tm_dy, tm_x;       // operand panels: boxes of 64 columns x one stage of token rows
+  CUtensorMap tm_w, tm_m, tm_v;  // boxes of 128 rows x one swizzle row of a chunk, for the loads and the stores
   int BT, V, H;
   int num_kb;          // ceil(BT / BK)
   int tiles_m;         // row tiles of TILE_M * CG rows
   int tiles_n;         // column tiles of TILE_N columns
-  int split_from;      // units below this are whole tiles; the rest are 128-column halves of the following tiles
-  int num_units;       // = clusters in the grid
+  int unit_base;       // number of this problem's first unit in the launch
+  int split_from;      // units (counted from unit_base) below this are whole tiles; the rest are 128-column halves of the following tiles
+  int num_units;
+  int ld_scale;        // row pitch of the scale arrays, in floats
   const uint8_t* dy;   // bf16 operands as the tensor maps see them (for the start-up L2 prefetch)
   const uint8_t* x;
   long long ld_dy_bytes, ld_x_bytes;
-  Hyper hyper;
   float* m_scale;      // int8 / fp8-block: (V, H/64) row-major; fp8-tensor: one scalar
   float* v_scale;
-  int ld_scale;        // row pitch of the scale arrays, in floats
   float* m_absmax;     // fp8-tensor: next-step absmax accumulators (atomic max)
   float* v_absmax;
-  int* status;         // device status word: 0 = ok
   const Hyper* hyper_dev;  // optional: hyper-parameters read from device memory instead of `hyper`
+  Hyper hyper;
+};
+
+struct WgradGroup {
+  int n;               // problems in this launch
+  int num_units;       // = clusters in the grid
+  int* status;         // device status word: 0 = ok
+  WgradProblem prob[MAX_GROUP];
 };
 
 // bytes one pipeline stage of W + moments takes for a chunk of `cn` columns
@@ -294,10 +312,7 @@ constexpr int TQ_READERS_PER_CTA = 3 + NUM_EPI_WARPS;
 // ------------------------------------------------------------------------------------------------
 template <int W_DT, int ST, int OPT, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_x,
-                   const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_m,
-                   const __grid_constant__ CUtensorMap tm_v, const WgradParams p) {
-  // tm_w/m/v: boxes of 128 rows x one swizzle row of a chunk, used for the loads and the stores
+forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
   using Cfg = WgradCfg<W_DT, ST, OPT, CG>;
   constexpr int BK = Cfg::kBK;
   constexpr int NSTAGE = Cfg::kNStage;
@@ -353,11 +368,21 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
       tmem_relinquish();
     }
   }
-  if (warp == 0 && lane == 0) { prefetch_tmap(&tm_dy); prefetch_tmap(&tm_x); }
-  if (warp == 2 && lane == 0) {
-    prefetch_tmap(&tm_w);
-    if (NMOM > 0) prefetch_tmap(&tm_m);
-    if (NMOM > 1) prefetch_tmap(&tm_v);
+  // Problem a unit belongs to.  Units are numbered problem after problem; a launch has at most
+  // MAX_GROUP problems, so a short scan does.
+  auto locate = [&](int unit) -> const WgradProblem* {
+    int i = 0;
+    while (i + 1 < gp.n && unit >= gp.prob[i + 1].unit_base) ++i;
+    return &gp.prob[i];
+  };
+  {
+    const WgradProblem* p0 = locate(first_unit);
+    if (warp == 0 && lane == 0) { prefetch_tmap(&p0->tm_dy); prefetch_tmap(&p0->tm_x); }
+    if (warp == 2 && lane == 0) {
+      prefetch_tmap(&p0->tm_w);
+      if (NMOM > 0) prefetch_tmap(&p0->tm_m);
+      if (NMOM > 1) prefetch_tmap(&p0->tm_v);
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -365,17 +390,20 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
 
-  // unit number -> row tile, first column, width (TILE_N, or TILE_N / 2 for a half)
+  // unit number -> problem, row tile, first column, width (TILE_N, or TILE_N / 2 for a half)
+  const WgradProblem* pp = nullptr;
   auto decode_unit = [&](int unit, int& row_tile, int& col0, int& ncols) {
-    int tile = unit, half = 0;
+    pp = locate(unit);
+    const int u = unit - pp->unit_base;
+    int tile = u, half = 0;
     ncols = TILE_N;
-    if (unit >= p.split_from) {
-      tile = p.split_from + ((unit - p.split_from) >> 1);
-      half = (unit - p.split_from) & 1;
+    if (u >= pp->split_from) {
+      tile = pp->split_from + ((u - pp->split_from) >> 1);
+      half = (u - pp->split_from) & 1;
       ncols = TILE_N / 2;
     }
-    row_tile = tile / p.tiles_n;
-    col0 = (tile - row_tile * p.tiles_n) * TILE_N + half * (TILE_N / 2);
+    row_tile = tile / pp->tiles_n;
+    col0 = (tile - row_tile * pp->tiles_n) * TILE_N + half * (TILE_N / 2);
   };
   // the leader CTA's tq_empty[0], where every reader of the cluster reports that it has taken a unit
   const uint32_t tq_empty0 = (CG == 2) ? map_to_cta(smem_u32(&ctrl->tq_empty[0]), 0) : smem_u32(&ctrl->tq_empty[0]);
@@ -401,6 +429,7 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
       int unit = first_unit;
       bool more = true;        // the last request was answered with a unit
       uint32_t req = 0;        // requests answered so far
+      bool gate_open = false;  // the state producer has been told that the first unit's loads are queued
       if (cta_rank == 0) {
         mbar_expect_tx(&ctrl->clc_bar, 16);
         clc_try_cancel(&ctrl->clc_resp, &ctrl->clc_bar);
@@ -426,7 +455,10 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
         const int row0 = row_tile * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
         const int b_cols = ncols / CG;             // columns of the X panel this CTA stages
         const uint32_t b_bytes = static_cast<uint32_t>(b_cols) * BK * 2;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+        const int num_kb = pp->num_kb;
+        const CUtensorMap* tm_dy = &pp->tm_dy;
+        const CUtensorMap* tm_x = &pp->tm_x;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % NSTAGE;
           const uint32_t ph = (it / NSTAGE) & 1;
           if (!mbar_wait(&ctrl->op_empty[s], ph ^ 1, abort_word, ERR_WAIT_OP_EMPTY)) goto done;
@@ -439,19 +471,19 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             const int bcol0 = col0 + static_cast<int>(cta_rank) * b_cols;
 #pragma unroll
             for (int i = 0; i < TILE_M / 64; ++i)
-              tma_load_2d_pair(a + i * SLAB_BYTES, &tm_dy, full_leader, row0 + 64 * i, kb * BK, pol);
+              tma_load_2d_pair(a + i * SLAB_BYTES, tm_dy, full_leader, row0 + 64 * i, kb * BK, pol);
             for (int i = 0; i < b_cols / 64; ++i)
-              tma_load_2d_pair(b + i * SLAB_BYTES, &tm_x, full_leader, bcol0 + 64 * i, kb * BK, pol);
+              tma_load_2d_pair(b + i * SLAB_BYTES, tm_x, full_leader, bcol0 + 64 * i, kb * BK, pol);
           } else {
             mbar_expect_tx(&ctrl->op_full[s], A_BYTES + b_bytes);
 #pragma unroll
             for (int i = 0; i < TILE_M / 64; ++i)
-              tma_load_2d(a + i * SLAB_BYTES, &tm_dy, &ctrl->op_full[s], row0 + 64 * i, kb * BK, pol);
+              tma_load_2d(a + i * SLAB_BYTES, tm_dy, &ctrl->op_full[s], row0 + 64 * i, kb * BK, pol);
             for (int i = 0; i < b_cols / 64; ++i)
-              tma_load_2d(b + i * SLAB_BYTES, &tm_x, &ctrl->op_full[s], col0 + 64 * i, kb * BK, pol);
+              tma_load_2d(b + i * SLAB_BYTES, tm_x, &ctrl->op_full[s], col0 + 64 * i, kb * BK, pol);
           }
         }
-        if (it == static_cast<uint32_t>(p.num_kb)) mbar_arrive(&ctrl->fill_gate);   // end of the first unit
+        if (!gate_open) { mbar_arrive(&ctrl->fill_gate); gate_open = true; }   // end of the first unit
         if (cta_rank == 0) {
           // the answer to the request made one unit ago has had a whole tile's loads to arrive
           if (more) {
@@ -484,7 +516,8 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
         if (!mbar_wait(&ctrl->acc_empty[buf], aph ^ 1, abort_word, ERR_WAIT_ACC_EMPTY)) goto done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * TILE_N;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+        const int num_kb = pp->num_kb;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % NSTAGE;
           const uint32_t ph = (it / NSTAGE) & 1;
           if (!mbar_wait(&ctrl->op_full[s], ph, abort_word, ERR_WAIT_OP_FULL)) goto done;
@@ -520,15 +553,18 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
         decode_unit(unit, row_tile, col0, ncols);
         const int row0 = row_tile * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
         const int nch = ncols / CN;
+        const CUtensorMap* tm_w = &pp->tm_w;
+        const CUtensorMap* tm_m = &pp->tm_m;
+        const CUtensorMap* tm_v = &pp->tm_v;
         if constexpr (ST == ST_INT8 || ST == ST_FP8_BLOCK) {
           // The epilogue threads read their rows' block scales straight from global memory at the top
           // of a tile; this thread knows the tile several microseconds earlier and pulls the lines
           // into L2 (one 16-byte group of scales per row, tensor and tile).
           for (int rr = 0; rr < TILE_M; ++rr) {
-            if (row0 + rr < p.V) {
-              const size_t off = static_cast<size_t>(row0 + rr) * p.ld_scale + (col0 >> 6);
-              prefetch_l2(p.m_scale + off);
-              prefetch_l2(p.v_scale + off);
+            if (row0 + rr < pp->V) {
+              const size_t off = static_cast<size_t>(row0 + rr) * pp->ld_scale + (col0 >> 6);
+              prefetch_l2(pp->m_scale + off);
+              prefetch_l2(pp->v_scale + off);
             }
           }
         }
@@ -540,7 +576,7 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           // of state loads ahead of the first tile's panels doubles the time to the first accumulator
           // (8 us instead of 4).  Two chunks are enough for the epilogue to start on; the rest wait
           // until the producer has queued the whole first panel.
-          if (q == FORGE_FILL_GATE_CHUNKS && p.num_kb > 0) {
+          if (q == FORGE_FILL_GATE_CHUNKS) {
             if (!mbar_wait(&ctrl->fill_gate, 0, abort_word, ERR_WAIT_FILL_GATE)) goto done;
           }
           uint8_t* wb = st_buf + s * Cfg::kStageBytes;
@@ -548,18 +584,18 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           const int cc = col0 + c * CN;
 #pragma unroll
           for (int bx = 0; bx < BoxGeom<WRB>::kBoxes; ++bx)
-            tma_load_2d(wb + bx * BoxGeom<WRB>::kBoxBytes, &tm_w, &ctrl->st_full[s], cc + bx * WBC, row0, pol);
+            tma_load_2d(wb + bx * BoxGeom<WRB>::kBoxBytes, tm_w, &ctrl->st_full[s], cc + bx * WBC, row0, pol);
           if constexpr (NMOM > 0) {
             uint8_t* mb = wb + Cfg::kWBytes;
 #pragma unroll
             for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-              tma_load_2d(mb + bx * BoxGeom<SRB>::kBoxBytes, &tm_m, &ctrl->st_full[s], cc + bx * SBC, row0, pol);
+              tma_load_2d(mb + bx * BoxGeom<SRB>::kBoxBytes, tm_m, &ctrl->st_full[s], cc + bx * SBC, row0, pol);
           }
           if constexpr (NMOM > 1) {
             uint8_t* vb = wb + Cfg::kWBytes + Cfg::kSBytes;
 #pragma unroll
             for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-              tma_load_2d(vb + bx * BoxGeom<SRB>::kBoxBytes, &tm_v, &ctrl->st_full[s], cc + bx * SBC, row0, pol);
+              tma_load_2d(vb + bx * BoxGeom<SRB>::kBoxBytes, tm_v, &ctrl->st_full[s], cc + bx * SBC, row0, pol);
           }
         }
       }
@@ -574,6 +610,10 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
         decode_unit(unit, row_tile, col0, ncols);
         const int row0 = row_tile * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
         const int nch = ncols / CN;
+        const CUtensorMap* tm_w = &pp->tm_w;
+        const CUtensorMap* tm_m = &pp->tm_m;
+        const CUtensorMap* tm_v = &pp->tm_v;
+        const int pV = pp->V, pH = pp->H;
         for (int c = 0; c < nch; ++c, ++q) {
           const int s = q % NSS;
           const uint32_t ph = (q / NSS) & 1;
@@ -582,21 +622,21 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           if (!mbar_wait(&ctrl->st_done[s], ph, abort_word, ERR_WAIT_ST_DONE)) goto done;
           uint8_t* wb = st_buf + s * Cfg::kStageBytes;
           const int cc = col0 + c * CN;
-          if (row0 < p.V && cc < p.H) {   // rows / columns past the edge of a started box are clipped
+          if (row0 < pV && cc < pH) {   // rows / columns past the edge of a started box are clipped
 #pragma unroll
             for (int bx = 0; bx < BoxGeom<WRB>::kBoxes; ++bx)
-              if (cc + bx * WBC < p.H) tma_store_2d(&tm_w, wb + bx * BoxGeom<WRB>::kBoxBytes, cc + bx * WBC, row0, pol);
+              if (cc + bx * WBC < pH) tma_store_2d(tm_w, wb + bx * BoxGeom<WRB>::kBoxBytes, cc + bx * WBC, row0, pol);
             if constexpr (NMOM > 0) {
               uint8_t* mb = wb + Cfg::kWBytes;
 #pragma unroll
               for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-                if (cc + bx * SBC < p.H) tma_store_2d(&tm_m, mb + bx * BoxGeom<SRB>::kBoxBytes, cc + bx * SBC, row0, pol);
+                if (cc + bx * SBC < pH) tma_store_2d(tm_m, mb + bx * BoxGeom<SRB>::kBoxBytes, cc + bx * SBC, row0, pol);
             }
             if constexpr (NMOM > 1) {
               uint8_t* vb = wb + Cfg::kWBytes + Cfg::kSBytes;
 #pragma unroll
               for (int bx = 0; bx < BoxGeom<SRB>::kBoxes; ++bx)
-                if (cc + bx * SBC < p.H) tma_store_2d(&tm_v, vb + bx * BoxGeom<SRB>::kBoxBytes, cc + bx * SBC, row0, pol);
+                if (cc + bx * SBC < pH) tma_store_2d(tm_v, vb + bx * BoxGeom<SRB>::kBoxBytes, cc + bx * SBC, row0, pol);
             }
           }
           tma_store_commit();
@@ -612,15 +652,28 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
     const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
     const int wg = (warp - EPI_WARP0) >> 2;       // 0 or 1
     const int r = quarter * 32 + lane;            // row inside the tile
-    const Hyper hy = (p.hyper_dev != nullptr) ? *p.hyper_dev : p.hyper;
+    // per-problem values, (re)loaded when the unit at hand belongs to another problem than the last
+    const WgradProblem* cur = nullptr;
+    Hyper hy = gp.prob[0].hyper;
     float s_m_t = 1.0f, s_v_t = 1.0f, inv_m_t = 1.0f, inv_v_t = 1.0f;
     float amax_m_t = 0.0f, amax_v_t = 0.0f;
-    if constexpr (ST == ST_FP8_TENSOR) {
-      s_m_t = *p.m_scale;
-      s_v_t = *p.v_scale;
-      inv_m_t = f_div(1.0f, s_m_t);
-      inv_v_t = f_div(1.0f, s_v_t);
-    }
+    // fp8 per tensor: this warp's running maxima of |m'| and |v'| go to the problem's accumulators
+    auto flush_absmax = [&](const WgradProblem* q) {
+      if constexpr (ST == ST_FP8_TENSOR) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          amax_m_t = fmaxf(amax_m_t, __shfl_xor_sync(0xffffffffu, amax_m_t, o));
+          amax_v_t = fmaxf(amax_v_t, __shfl_xor_sync(0xffffffffu, amax_v_t, o));
+        }
+        if (lane == 0) {
+          // non-negative floats order like their bit patterns
+          atomicMax(reinterpret_cast<unsigned int*>(q->m_absmax), __float_as_uint(amax_m_t));
+          atomicMax(reinterpret_cast<unsigned int*>(q->v_absmax), __float_as_uint(amax_v_t));
+        }
+        amax_m_t = 0.0f;
+        amax_v_t = 0.0f;
+      }
+    };
     uint32_t tile_it = 0;
     uint32_t q_base = 0;   // chunks of the tiles before this one (always even)
     bool ok = true;
@@ -629,21 +682,21 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
     // the first tile would take three to four DRAM round trips; these 256 idle threads ask L2 for
     // the whole panel of the first unit at once instead (the unit of a cluster's own index is known
     // without the queue).
-    if (p.num_kb > 0) {
-      decode_unit(first_unit, row_tile, col0, ncols);
+    decode_unit(first_unit, row_tile, col0, ncols);
+    if (pp->num_kb > 0) {
       const int a_col0 = row_tile * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
       const int b_cols = ncols / CG;
       const int b_col0 = col0 + static_cast<int>(cta_rank) * ((CG == 2) ? b_cols : 0);
       const int lines_a = TILE_M / 64, per_row = lines_a + b_cols / 64;   // 128-byte lines per token row
-      const int rows = p.BT < 1024 ? p.BT : 1024;
+      const int rows = pp->BT < 1024 ? pp->BT : 1024;
       for (int idx = static_cast<int>(threadIdx.x) - EPI_WARP0 * 32; idx < rows * per_row; idx += NUM_EPI_WARPS * 32) {
         const int row = idx / per_row, l = idx - row * per_row;
         if (l < lines_a) {
           const int col = a_col0 + 64 * l;
-          if (col < p.V) prefetch_l2(p.dy + row * p.ld_dy_bytes + col * 2);
+          if (col < pp->V) prefetch_l2(pp->dy + row * pp->ld_dy_bytes + col * 2);
         } else {
           const int col = b_col0 + 64 * (l - lines_a);
-          if (col < p.H) prefetch_l2(p.x + row * p.ld_x_bytes + col * 2);
+          if (col < pp->H) prefetch_l2(pp->x + row * pp->ld_x_bytes + col * 2);
         }
       }
     }
@@ -662,6 +715,18 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
       ++tq_pos;
       if (unit < 0) break;
       decode_unit(unit, row_tile, col0, ncols);
+      if (pp != cur) {
+        if (cur != nullptr) flush_absmax(cur);
+        cur = pp;
+        hy = (pp->hyper_dev != nullptr) ? *pp->hyper_dev : pp->hyper;
+        if constexpr (ST == ST_FP8_TENSOR) {
+          s_m_t = *pp->m_scale;
+          s_v_t = *pp->v_scale;
+          inv_m_t = f_div(1.0f, s_m_t);
+          inv_v_t = f_div(1.0f, s_v_t);
+        }
+      }
+      const int pV = pp->V, pH = pp->H;
       const int row0 = row_tile * (TILE_M * CG) + static_cast<int>(cta_rank) * TILE_M;
       const int half_chunks = ncols / (2 * CN);   // chunks of this tile per epilogue group
       const int buf = tile_it & 1;
@@ -674,9 +739,9 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           const int cb = (col0 >> 6) + wg + 2 * i;
-          if (grow < p.V && cb * 64 < p.H) {
-            sc_m[i] = __ldg(p.m_scale + static_cast<size_t>(grow) * p.ld_scale + cb);
-            sc_v[i] = __ldg(p.v_scale + static_cast<size_t>(grow) * p.ld_scale + cb);
+          if (grow < pV && cb * 64 < pH) {
+            sc_m[i] = __ldg(pp->m_scale + static_cast<size_t>(grow) * pp->ld_scale + cb);
+            sc_v[i] = __ldg(pp->v_scale + static_cast<size_t>(grow) * pp->ld_scale + cb);
           }
         }
       }
@@ -716,7 +781,7 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
             else mbar_arrive(&ctrl->acc_empty[buf]);
           }
         }
-        if (p.num_kb == 0) {
+        if (pp->num_kb == 0) {
 #pragma unroll
           for (int k = 0; k < CN; ++k) acc[k] = 0u;
         }
@@ -894,9 +959,9 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
           }
           {
             const int cb = (col0 >> 6) + c;
-            if (grow < p.V && cb * 64 < p.H) {
-              p.m_scale[static_cast<size_t>(grow) * p.ld_scale + cb] = sm_new;
-              p.v_scale[static_cast<size_t>(grow) * p.ld_scale + cb] = sv_new;
+            if (grow < pV && cb * 64 < pH) {
+              pp->m_scale[static_cast<size_t>(grow) * pp->ld_scale + cb] = sm_new;
+              pp->v_scale[static_cast<size_t>(grow) * pp->ld_scale + cb] = sv_new;
             }
           }
         } else {  // ST_FP8_TENSOR
@@ -943,18 +1008,7 @@ forge_wgrad_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_const
       if (!ok) break;
       q_base += 2 * half_chunks;
     }
-    if constexpr (ST == ST_FP8_TENSOR) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        amax_m_t = fmaxf(amax_m_t, __shfl_xor_sync(0xffffffffu, amax_m_t, o));
-        amax_v_t = fmaxf(amax_v_t, __shfl_xor_sync(0xffffffffu, amax_v_t, o));
-      }
-      if (lane == 0) {
-        // non-negative floats order like their bit patterns
-        atomicMax(reinterpret_cast<unsigned int*>(p.m_absmax), __float_as_uint(amax_m_t));
-        atomicMax(reinterpret_cast<unsigned int*>(p.v_absmax), __float_as_uint(amax_v_t));
-      }
-    }
+    if (cur != nullptr) flush_absmax(cur);
   }
 
 done:
@@ -968,7 +1022,7 @@ done:
     // error path: give copies in flight a bounded time to land before shared memory is released
     const long long t0 = clock64();
     while (clock64() - t0 < 400000) __nanosleep(1000);
-    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
+    if (threadIdx.x == 0 && gp.status != nullptr) atomicCAS(gp.status, 0, *abort_word);
     __syncthreads();
   }
   // a pair leaves together: the peer's shared memory and barriers stay valid until both are done

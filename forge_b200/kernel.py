@@ -12,6 +12,7 @@ Additions with no reference counterpart: SGD with momentum, Lion, e4m3 moments w
 from __future__ import annotations
 
 import ctypes
+import threading
 
 import torch
 
@@ -25,16 +26,20 @@ from forge_b200._lib import (
 FP8_E4M3_MAX = 448.0
 FP8_E5M2_MAX = 57344.0
 
-# scratch for fp32 operands, one growing buffer per device (the library itself allocates nothing)
-_scratch: dict[int, torch.Tensor] = {}
+# Scratch for fp32 operands (the library itself allocates nothing on this path): one growing buffer per
+# (device, stream).  Updates on different streams may overlap on the GPU, so they must not share the
+# split area; on one stream launches are ordered, and the caching allocator only hands a dropped
+# buffer's memory to later work of the stream that allocated it.
+_scratch: dict[tuple, torch.Tensor] = {}
 
 
 def _get_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    buf = _scratch.get(idx)
+    key = (idx, torch.cuda.current_stream(device).cuda_stream)
+    buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        _scratch[idx] = buf
+        _scratch[key] = buf
     return buf
 
 
@@ -84,8 +89,9 @@ class DeviceHyper:
     """Hyper-parameters kept in device memory so that captured CUDA graphs can be replayed with a
     new lr / step: ``update(...)`` packs them on the host (same narrowing as the direct path) and
     enqueues one 64-byte copy on the current stream; pass the object as ``hyper_device=`` to the
-    fused operators.  The pinned staging area is a small ring, so an update never overwrites bytes
-    that a copy enqueued for an earlier step may not have read yet."""
+    fused operators.  The pinned staging area is a ring of ``RING`` slots; an event recorded after
+    each copy guards its slot, and ``update`` waits for that event before it rewrites the slot, so a
+    host that runs many steps ahead of the GPU never overwrites bytes a queued copy has not read."""
 
     NBYTES = 64
     RING = 16
@@ -93,24 +99,127 @@ class DeviceHyper:
     def __init__(self, device):
         self.host = torch.zeros(self.RING, self.NBYTES, dtype=torch.uint8).pin_memory()
         self.dev = torch.zeros(self.NBYTES, dtype=torch.uint8, device=device)
+        self._copied = [None] * self.RING     # event after the last copy that read each slot
         self._n = 0
 
     def update(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1, momentum=0.0, nesterov=False):
         h = _hyper(lr, beta1, beta2, eps, weight_decay, step, momentum, nesterov)
-        slot = self.host[self._n % self.RING]
+        i = self._n % self.RING
         self._n += 1
+        capturing = torch.cuda.is_current_stream_capturing()
+        ev = self._copied[i]
+        if ev is not None and not capturing:
+            ev.synchronize()                  # the copy that last read this slot has run
+        slot = self.host[i]
         _lib.check(_lib.load().forge_hyper_pack(ctypes.byref(h), slot.data_ptr()), "forge_hyper_pack")
-        self.dev.copy_(slot, non_blocking=True)
+        with torch.cuda.device(self.dev.device):
+            self.dev.copy_(slot, non_blocking=True)
+            if not capturing:
+                if ev is None:
+                    ev = self._copied[i] = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream(self.dev.device))
         return self
 
     def data_ptr(self):
         return self.dev.data_ptr()
 
 
+class UpdateGroup:
+    """Fused updates of several weights issued together (``forge_wgrad_update_group``): consecutive
+    entries of one kernel configuration share a launch, eight at most, so the fixed start-up and the
+    ragged end of a launch are paid once per group.  No reference counterpart: the reference launches
+    one kernel per linear (``autograd.py:94-144``).
+
+        with UpdateGroup() as g:                       # calls inside are recorded, not launched
+            fused_grad_adamw(dy_q, x, w_q, m_q, v_q, lr=lr, step=t)
+            fused_grad_adamw(dy_k, x, w_k, m_k, v_k, lr=lr, step=t)
+        # leaving the block enqueues one launch on the current stream
+
+    ``record()`` / ``flush()`` give the same in two steps for callers (the autograd function of
+    ``FusedLinear``) that collect entries over several backward nodes.  The group keeps the recorded
+    activations alive until ``flush`` has enqueued the launch.  Each weight's result is bit-identical
+    to its own single launch.  Put the largest weights first: work units follow the recorded order.
+    """
+
+    def __init__(self):
+        self._args: list[ForgeWgradArgs] = []
+        self._keep: list = []
+        self._device = None
+
+    def __len__(self):
+        return len(self._args)
+
+    def record(self):
+        """Context manager: fused_grad_* calls made by this thread inside it are added to the group."""
+        return _Recording(self)
+
+    def __enter__(self):
+        self._rec = _Recording(self)
+        self._rec.__enter__()
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        self._rec.__exit__(exc_type, exc, tb)
+        if exc_type is None:
+            self.flush()
+        else:
+            self.clear()
+        return False
+
+    def _add(self, a: ForgeWgradArgs, device, keep):
+        if self._device is not None and device != self._device:
+            raise ValueError("an UpdateGroup holds weights of one device")
+        self._device = device
+        c = ForgeWgradArgs()
+        ctypes.memmove(ctypes.byref(c), ctypes.byref(a), ctypes.sizeof(ForgeWgradArgs))
+        self._args.append(c)
+        self._keep.append(keep)
+
+    def clear(self):
+        self._args.clear()
+        self._keep.clear()
+        self._device = None
+
+    def flush(self):
+        """Enqueue the recorded updates on the current stream of their device and forget them."""
+        n = len(self._args)
+        if n == 0:
+            return
+        arr = (ForgeWgradArgs * n)(*self._args)
+        dev = self._device
+        lib = _lib.load()
+        try:
+            with torch.cuda.device(dev):
+                rc = lib.forge_wgrad_update_group(arr, n, _lib.current_stream_ptr(dev))
+        finally:
+            self.clear()
+        if rc:
+            _lib.check(rc, "forge_wgrad_update_group")
+
+
+_recording = threading.local()
+
+
+class _Recording:
+    def __init__(self, group):
+        self.group = group
+
+    def __enter__(self):
+        self.prev = getattr(_recording, "group", None)
+        _recording.group = self.group
+        return self.group
+
+    def __exit__(self, *exc):
+        _recording.group = self.prev
+        return False
+
+
 def _wgrad(grad_output, input, weight, optimizer, state, hyper, hyper_device=None):
     if not (grad_output.is_cuda and input.is_cuda and weight.is_cuda):
         _require_cuda(grad_output, input, weight)
-    assert grad_output.is_contiguous() and input.is_contiguous()
+    if not (grad_output.is_contiguous() and input.is_contiguous()):
+        # AssertionError as in the reference (kernel.py:1363), raised explicitly so that it survives `python -O`
+        raise AssertionError("grad_output and input must be contiguous (row pitches V and H)")
     BT, V = grad_output.shape
     H = input.shape[1]
     odt = grad_output.dtype
@@ -144,12 +253,18 @@ def _wgrad(grad_output, input, weight, optimizer, state, hyper, hyper_device=Non
     a.state = state
     a.hyper = hyper
     a.hyper_device = hyper_device.data_ptr() if hyper_device is not None else None
+    group = getattr(_recording, "group", None)
     scratch = None
     if odt != torch.bfloat16:
         nbytes = lib.forge_wgrad_scratch_bytes(BT, V, H, a.operand_dtype)
-        scratch = _get_scratch(weight.device, nbytes)
+        # a recorded entry keeps a split area of its own until the group's launch has been enqueued
+        scratch = (torch.empty(nbytes, dtype=torch.uint8, device=weight.device) if group is not None
+                   else _get_scratch(weight.device, nbytes))
         a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
     dev = weight.device
+    if group is not None:
+        group._add(a, dev, (grad_output, input, weight, scratch, hyper_device))
+        return
     if dev.index == torch.cuda.current_device():
         rc = lib.forge_wgrad_update(ctypes.byref(a), torch.cuda.current_stream().cuda_stream)
     else:
@@ -161,7 +276,8 @@ def _wgrad(grad_output, input, weight, optimizer, state, hyper, hyper_device=Non
 
 def _optim(grad, weight, optimizer, state, hyper):
     _require_cuda(grad, weight)
-    assert grad.is_contiguous()
+    if not grad.is_contiguous():
+        raise AssertionError("grad must be contiguous")
     _row_major_2d(weight, "weight")
     V, H = weight.shape
     if tuple(grad.shape) != (V, H):
@@ -221,7 +337,8 @@ def optimizer_only_adamw(grad, weight, m, v, lr: float = 1e-4, beta1: float = 0.
 
 def _int8_state(weight, m_q, v_q, m_scale, v_scale, qblock, mode=ST_INT8):
     H = weight.shape[1]
-    assert H % qblock == 0, f"H ({H}) must be divisible by qblock ({qblock})"
+    if H % qblock != 0:
+        raise AssertionError(f"H ({H}) must be divisible by qblock ({qblock})")   # kernel.py:1513
     _require_cuda(m_q, v_q, m_scale, v_scale)
     _row_major_2d(m_q, "m_q")
     _row_major_2d(v_q, "v_q")

@@ -32,7 +32,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from forge_b200.autograd import FusedLinearFunction
+from forge_b200.autograd import FusedLinearFunction, LayerUpdateGroup
 from forge_b200.state import FusedOptimizerState, OptimizerConfig
 
 
@@ -69,6 +69,8 @@ class FusedLinear(nn.Module):
         self._l2_manager = None
         # False: materialise grad_W with a library GEMM and run the optimizer-only kernel
         self.use_fused_backward = True
+        # set by FusedOptimizerManager.group_updates: the launch this module's update is issued with
+        self._update_group = None
 
     @classmethod
     def from_linear(cls, linear: nn.Linear, optimizer_type="adamw", quantize_state=False,
@@ -105,7 +107,7 @@ class FusedLinear(nn.Module):
         self._ensure_state()
         return FusedLinearFunction.apply(x, self.weight, self.bias, self._state, self._config,
                                          self._is_accumulating, self._l2_manager,
-                                         self.use_fused_backward)
+                                         self.use_fused_backward, self._update_group)
 
     def get_optimizer_state_dict(self):
         return None if self._state is None else self._state.state_dict()
@@ -133,7 +135,9 @@ class FusedOptimizerManager:
         self._global_step = 0
         self._micro_step = 0
         self._l2_manager = None  # accepted for signature compatibility; see the module docstring
-        self._device_hyper = {}   # optimizer type -> DeviceHyper, see enable_device_hyper
+        self._update_groups: list[LayerUpdateGroup] = []   # see group_updates
+        self._device_hyper = {}   # _group_key -> DeviceHyper, see enable_device_hyper
+        self._use_device_hyper = False
         self._fused_modules: list[FusedLinear] = []
         self._fused_module_names: dict[int, str] = {}
         self._fused_param_ids: set[int] = set()
@@ -164,16 +168,21 @@ class FusedOptimizerManager:
             self._global_step += 1
         if lr is None:
             lr = 1e-4
-        # one shared config per distinct (optimizer, constructor keywords) instead of one per module
+        for g in self._update_groups:      # nothing recorded in an earlier pass may wait any longer
+            g.flush()
+        # one shared config per distinct (optimizer, constructor keywords, device) instead of one per module
         configs: dict[tuple, OptimizerConfig] = {}
         for m in self._fused_modules:
-            key = (m.optimizer_type, tuple(sorted(m.optimizer_kwargs.items())))
+            key = self._group_key(m)
             cfg = configs.get(key)
             if cfg is None:
                 cfg = OptimizerConfig(optimizer_type=m.optimizer_type,
                                       **{**m.optimizer_kwargs, **kwargs, "lr": lr})
-                hd = self._device_hyper.get(m.optimizer_type)
-                if hd is not None and not is_accumulating:
+                if self._use_device_hyper and not is_accumulating:
+                    hd = self._device_hyper.get(key)
+                    if hd is None:      # a group that appeared after enable_device_hyper()
+                        from forge_b200.kernel import DeviceHyper
+                        hd = self._device_hyper[key] = DeviceHyper(m.weight.device)
                     hd.update(lr=cfg.lr, beta1=cfg.beta1, beta2=cfg.beta2, eps=cfg.eps,
                               weight_decay=cfg.weight_decay, step=max(self._global_step, 1),
                               momentum=cfg.momentum, nesterov=cfg.nesterov)
@@ -182,18 +191,79 @@ class FusedOptimizerManager:
             m._config = cfg
             m._is_accumulating = is_accumulating
 
+    @staticmethod
+    def _group_key(m: "FusedLinear") -> tuple:
+        """Modules that share this key train with the same hyper-parameters on the same device."""
+        return (m.optimizer_type, tuple(sorted(m.optimizer_kwargs.items())), str(m.weight.device))
+
     def enable_device_hyper(self, device=None):
-        """Keep the step's hyper-parameters in device memory (one 64-byte block per optimizer type,
-        rewritten by ``pre_step``) so that a CUDA graph holding the backward pass can be replayed with
-        a new lr and step count.  The step count is the manager's global step; every fused parameter
-        is assumed to be updated on every non-accumulating step.  No reference counterpart."""
+        """Keep the step's hyper-parameters in device memory -- one 64-byte block per distinct
+        (optimizer type, constructor keywords, device) of the fused modules, rewritten by
+        ``pre_step`` -- so that a CUDA graph holding the backward pass can be replayed with a new lr
+        and step count.  Modules built with different keywords (say ``weight_decay=0`` on some
+        layers) or living on different GPUs get blocks of their own.  The step count is the manager's
+        global step; every fused parameter is assumed to be updated on every non-accumulating step.
+        ``device`` is accepted for compatibility and ignored: a block lives where its modules do.
+        No reference counterpart."""
         from forge_b200.kernel import DeviceHyper
-        if device is None:
-            device = next(m.weight.device for m in self._fused_modules)
+        self._use_device_hyper = True
         for m in self._fused_modules:
-            if m.optimizer_type not in self._device_hyper:
-                self._device_hyper[m.optimizer_type] = DeviceHyper(device)
+            key = self._group_key(m)
+            if key not in self._device_hyper:
+                self._device_hyper[key] = DeviceHyper(m.weight.device)
         return self
+
+    def group_updates(self, groups="layer", max_group: int = 8):
+        """Issue the fused updates of several linears as ONE launch each (``forge_wgrad_update_group``):
+        the start-up and ragged end of a launch are then paid once per group instead of once per
+        weight, which is most of what the small projections (k, v; every row shard in tensor-parallel
+        mode) cost.  ``groups`` is a list of lists of ``FusedLinear`` modules, or ``"layer"``: modules
+        whose names share the prefix up to their last numeric component (``model.layers.17.`` ...)
+        form a group, largest weights first, at most ``max_group`` (<= 8) per launch.  Members must
+        share optimizer type, state mode, weight dtype and device.  A group launches when its last
+        member's backward has run; ``pre_step`` (and ``flush_updates``) issue anything left over.
+        Results are bit-identical to ungrouped launches.  No reference counterpart."""
+        if self._update_groups:
+            self.flush_updates()
+            for m in self._fused_modules:
+                m._update_group = None
+            self._update_groups = []
+        if groups == "layer":
+            by_prefix: dict[tuple, list[FusedLinear]] = {}
+            for m in self._fused_modules:
+                parts = self._fused_module_names[id(m)].split(".")
+                idx = [i for i, p in enumerate(parts) if p.isdigit()]
+                if not idx:
+                    continue
+                key = (".".join(parts[: idx[-1] + 1]), self._group_key(m), m.state_mode, m.weight.dtype)
+                by_prefix.setdefault(key, []).append(m)
+            groups = []
+            for members in by_prefix.values():
+                members = sorted(members, key=lambda m: -m.weight.numel())
+                groups += [members[i:i + max_group] for i in range(0, len(members), max_group)]
+        for members in groups:
+            members = list(members)
+            if len(members) < 2:
+                continue
+            if len(members) > 8:
+                raise ValueError("a group holds at most 8 linears")
+            first = members[0]
+            for m in members:
+                if not isinstance(m, FusedLinear) or id(m) not in self._fused_module_names:
+                    raise ValueError("group members must be FusedLinear modules of this manager's model")
+                if (m.optimizer_type, m.state_mode, m.weight.dtype, m.weight.device) != (
+                        first.optimizer_type, first.state_mode, first.weight.dtype, first.weight.device):
+                    raise ValueError("members of a group must share optimizer type, state mode, weight dtype and device")
+            g = LayerUpdateGroup([m.weight for m in members])
+            for m in members:
+                m._update_group = g
+            self._update_groups.append(g)
+        return self
+
+    def flush_updates(self):
+        """Issue every recorded, not yet launched fused update (see ``group_updates``)."""
+        for g in self._update_groups:
+            g.flush()
 
     def optimizer_state_dict(self) -> dict:
         modules = {}

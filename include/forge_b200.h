@@ -3,8 +3,10 @@
  * Plain C types only: device pointers, sizes, enums as int, hyper-parameters as float/double and a
  * CUDA stream passed as void*.  Every function returns FORGE_OK (0) or a negative FORGE_ERR_* code;
  * forge_last_error_string() gives the message of the last failure on the calling thread.  The
- * library allocates no device memory; every buffer belongs to the caller.  All launches go to the
- * stream the caller passes and return without synchronising.
+ * library allocates no device memory at run time; every buffer belongs to the caller.  (The library
+ * image carries one fixed array of FORGE_STATIC_SCRATCH_BYTES per GPU, used only by
+ * forge_wgrad_update_static_scratch.)  All launches go to the stream the caller passes and return
+ * without synchronising.
  *
  * Shapes follow the reference: dY is (BT, V) "grad_output", X is (BT, H) "input", W and the
  * optimizer moments are (V, H); all row-major with the last dimension contiguous.
@@ -19,7 +21,7 @@
 extern "C" {
 #endif
 
-#define FORGE_ABI_VERSION 2
+#define FORGE_ABI_VERSION 3
 
 /* error codes */
 #define FORGE_OK 0
@@ -123,6 +125,22 @@ int forge_hyper_pack(const ForgeHyper* h, void* out);
  * reads the same W on the same stream (src/fused_grad_optimizer/autograd.py:50-55). */
 int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream);
 
+/* Weights one kernel launch of forge_wgrad_update_group covers. */
+#define FORGE_MAX_GROUP 8
+
+/* The fused update of `count` weights in as few launches as possible: consecutive entries that agree
+ * in w_dtype, optimizer and state mode share one launch, FORGE_MAX_GROUP at most, so that the fixed
+ * start-up and ragged end of a launch are paid once per group instead of once per weight (the q / k /
+ * v projections of a layer, gate / up, or all seven projections of a decoder layer).  Entries may
+ * differ in BT, V, H, hyper-parameters and operands.  The reference launches one kernel per linear
+ * from _apply_fused (src/fused_grad_optimizer/autograd.py:94-144); this replaces a run of those
+ * calls.  Every entry is checked before anything is launched: on an error no weight has been
+ * touched.  The result of each weight is bit-identical to forge_wgrad_update on that entry alone.
+ * Entries must not alias each other's W or state.  The work units follow the order of the entries;
+ * put the largest weights first.  A kernel that abandons a wait reports through the first non-NULL
+ * `status` of its launch. */
+int forge_wgrad_update_group(const ForgeWgradArgs* args, int32_t count, void* cuda_stream);
+
 /* Bytes of scratch forge_wgrad_update needs for the given operand type (0 for bf16 operands; fp32
  * operands are split into bf16 high/low parts in scratch before the GEMM). */
 size_t forge_wgrad_scratch_bytes(int64_t BT, int64_t V, int64_t H, int32_t operand_dtype);
@@ -188,6 +206,13 @@ int forge_state_bytes(int32_t optimizer, int32_t mode, int64_t V, int64_t H, int
 /* Copies the device status word to the host after synchronising the stream and clears it.
  * Returns FORGE_OK, or FORGE_ERR_TIMEOUT with the kernel's code in *code_out. */
 int forge_read_status(int32_t* status, int32_t* code_out, void* cuda_stream);
+
+/* Self-test of the failure path, for test suites: launches one small kernel whose bounded wait (the
+ * same routine the update kernels wait with) is on a barrier nothing ever signals.  After `limit_ns`
+ * (1 ns .. 1 s) the wait gives up, the kernel writes code 190 to *status and ends normally; a following
+ * forge_read_status returns FORGE_ERR_TIMEOUT with that code and clears the word.  Nothing faults and
+ * the context stays usable.  No reference counterpart (the reference has no device-side waits). */
+int forge_selftest_wait_timeout(int32_t* status, uint64_t limit_ns, void* cuda_stream);
 
 /* Message of the last error on the calling thread (never NULL). */
 const char* forge_last_error_string(void);

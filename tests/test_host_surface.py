@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/forge_b200.h but not exported"
     assert sorted(_lib.EXPORTED_SYMBOLS) == declared
-    assert lib.forge_abi_version() == 2
+    assert lib.forge_abi_version() == 3
     assert isinstance(_lib.last_error(), str)
 
 

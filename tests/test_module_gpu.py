@@ -162,3 +162,57 @@ def test_manager_quantize_override_and_counts():
     net(torch.randn(8, 64, device=DEV)).sum().backward()
     assert net[0]._state.state_mode == "int8" and net[0]._state.m_q.dtype == torch.int8
     assert net[0]._config is net[2]._config
+
+
+def test_device_hyper_ring_survives_a_host_far_ahead_of_the_gpu():
+    """40 updates queued behind a busy GPU without a single synchronisation: every step must run with
+    its own bias corrections although the pinned staging ring has only 16 slots (a slot is rewritten
+    only after the copy that read it has run)."""
+    from forge_b200 import kernel as K
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(3)
+    BT, V, H = 64, 128, 256
+    dy = (torch.randn(BT, V, device=dev, generator=gen) * 1e-2).bfloat16()
+    x = torch.randn(BT, H, device=dev, generator=gen).bfloat16()
+    w0 = (torch.randn(V, H, device=dev, generator=gen) * 0.02).bfloat16()
+    ref, snaps_ref = [w0.clone(), torch.zeros_like(w0), torch.zeros_like(w0)], []
+    for step in range(1, 41):
+        K.fused_grad_adamw(dy, x, *ref, lr=1e-3 * step, weight_decay=0.01, step=step)
+        snaps_ref.append(ref[0].clone())
+    torch.cuda.synchronize()
+    hd = K.DeviceHyper(dev)
+    got, snaps = [w0.clone(), torch.zeros_like(w0), torch.zeros_like(w0)], []
+    torch.cuda._sleep(int(4e8))                 # keeps the GPU busy while the host queues everything
+    for step in range(1, 41):
+        hd.update(lr=1e-3 * step, weight_decay=0.01, step=step)
+        K.fused_grad_adamw(dy, x, *got, hyper_device=hd)
+        snaps.append(got[0].clone())
+    torch.cuda.synchronize()
+    for step, (a, b) in enumerate(zip(snaps_ref, snaps), 1):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), f"step {step} ran with another step's hyper-parameters"
+
+
+def test_device_hyper_blocks_follow_constructor_keywords():
+    """Two AdamW groups that differ in weight_decay must not share a device block."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(0)
+
+    def build():
+        torch.manual_seed(0)
+        net = torch.nn.Sequential(torch.nn.Linear(128, 128, bias=False), torch.nn.Linear(128, 128, bias=False)).to(dev).bfloat16()
+        net[0] = FusedLinear.from_linear(net[0], weight_decay=0.0)
+        net[1] = FusedLinear.from_linear(net[1], weight_decay=0.5)
+        return net
+
+    direct, blocks = build(), build()
+    m_direct = FusedOptimizerManager(direct)
+    m_blocks = FusedOptimizerManager(blocks).enable_device_hyper()
+    assert len(m_blocks._device_hyper) == 2
+    x = torch.randn(32, 128, device=dev).bfloat16()
+    for _ in range(3):
+        for net, mgr in ((direct, m_direct), (blocks, m_blocks)):
+            mgr.pre_step(lr=1e-2)
+            net(x).float().square().mean().backward()
+    torch.cuda.synchronize()
+    for a, b in zip(direct.parameters(), blocks.parameters()):
+        assert torch.equal(a.data.view(torch.int16), b.data.view(torch.int16))
