@@ -7,9 +7,12 @@ reference fuses -- 32 decoder layers x (q 4096x4096, k 1024x4096, v 1024x4096, o
 gate 14336x4096, up 14336x4096, down 4096x14336) plus lm_head 128256x4096 -- at BT = 512 tokens,
 bf16 weights and bf16 AdamW moments, random-initialised, synthetic activations X ~ N(0,1) and
 gradients dY ~ N(0, 1e-2) in bf16.  A *step* is one fused wgrad+AdamW update of each of the 225
-weights (one kernel launch each).  Every weight and its moments are distinct buffers (45 GB in
-total), so each launch streams cold state; only the small X / dY panels may sit in L2, as they do in
-training where the preceding kernel has just produced them.
+weights.  ``--group layer`` (default) issues the seven projections of a decoder layer as ONE kernel
+launch (``forge_wgrad_update_group``: 33 launches per step), ``--group x`` one launch per set of
+linears that share their input (q/k/v, gate/up), ``--group none`` one launch per weight as the
+reference does.  Every weight and its moments are distinct buffers (45 GB in total), so each launch
+streams cold state; only the small X / dY panels may sit in L2, as they do in training where the
+preceding kernel has just produced them.
 
 ``value``  ms per step with X / dY already resident in device memory (CUDA events around the K
            timed steps on the launching stream, max over ranks).
@@ -176,7 +179,7 @@ def run_reference(args):
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "bt": BT, "state": "fp32 W/m/v on the host (torch.optim.AdamW)",
                    "reference_path": "torch autograd + torch.optim.AdamW on CPU"},
-        "cpu_baseline": {"value": value, "unit": "ms/step", "cores": cores, "kind": "reference", "sample": desc},
+        "cpu_baseline": {"value": value, "unit": "ms/step", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": "ms/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
@@ -219,6 +222,17 @@ def run_forge(args):
             m = torch.zeros_like(w)
             v = torch.zeros_like(w)
         params.append((name, V, H, grp, r0, r1, w, m, v))
+
+    # launches: lists of indices into `params` whose updates are issued together
+    if args.group == "none":
+        launches_idx = [[i] for i in range(len(params))]
+    else:
+        keyed: dict[str, list[int]] = {}
+        for i, (name, V, H, grp, *_r) in enumerate(params):
+            key = grp if args.group == "x" else (name.split(".")[0] if "." in name else name)
+            keyed.setdefault(key, []).append(i)
+        # largest weights first inside a launch: the small ones fill the ragged end
+        launches_idx = [sorted(ix, key=lambda i: -(params[i][5] - params[i][4]) * params[i][2]) for ix in keyed.values()]
 
     def update(dy, x, w, m, v):
         if args.moments == "int8":
@@ -285,15 +299,17 @@ def run_forge(args):
                         ev.record(comm_stream)
                     gathered[grp] = (xg, ev)
                     last_grp = grp
-        for i, (name, V, H, grp, r0, r1, w, m, v) in enumerate(params):
-            st = lanes[i % n_streams]
-            if do_gather:
-                x, ev = gathered[grp]
-                st.wait_event(ev)
-            else:
-                x = x_full[H]
-            with torch.cuda.stream(st):
-                update(dys[r1 - r0], x, w, m, v)
+        for li, members in enumerate(launches_idx):
+            st = lanes[li % n_streams]
+            with torch.cuda.stream(st), K.UpdateGroup():
+                for i in members:
+                    name, V, H, grp, r0, r1, w, m, v = params[i]
+                    if do_gather:
+                        x, ev = gathered[grp]
+                        st.wait_event(ev)
+                    else:
+                        x = x_full[H]
+                    update(dys[r1 - r0], x, w, m, v)
         for st in side_streams + ([comm_stream] if do_gather else []):
             done = torch.cuda.Event()
             done.record(st)
@@ -321,7 +337,6 @@ def run_forge(args):
         copy_stream.wait_event(start)     # orders this step's copies after the previous step's kernels
         last_use.clear()
         h2d = 0
-        last_grp, xg = None, None
 
         def upload(src_dev, tag, slot):
             nonlocal h2d
@@ -337,30 +352,29 @@ def run_forge(args):
 
         # Linears of one group (q/k/v; gate/up) consume the same activation: X is uploaded once per
         # group, into staging sets that alternate per group; every linear uploads its own dY.
-        n_grp, x_d = -1, None
-        for i, (name, V, H, grp, r0, r1, w, m, v) in enumerate(params):
-            slot = i & 1
-            dy_d = upload(dys[r1 - r0], "dy", slot)
-            new_grp = grp != last_grp
-            if new_grp:
-                n_grp += 1
-                last_grp = grp
-                x_d = upload(x_shard[H] if do_gather else x_full[H], "x", n_grp & 1)
+        # two staging sets, alternating per launch; inside a launch every member has buffers of its own
+        for li, members in enumerate(launches_idx):
+            slot = li & 1
+            staged_in, x_by_grp = [], {}
+            for k, i in enumerate(members):
+                name, V, H, grp, r0, r1, w, m, v = params[i]
+                dy_d = upload(dys[r1 - r0], ("dy", k), slot)
+                if grp not in x_by_grp:
+                    x_by_grp[grp] = upload(x_shard[H] if do_gather else x_full[H], ("x", len(x_by_grp)), slot)
+                staged_in.append((dy_d, x_by_grp[grp]))
             ready = torch.cuda.Event()
             ready.record(copy_stream)
             main.wait_event(ready)
-            used = [dy_d, x_d]
-            if do_gather:
-                if new_grp:
-                    xg = all_gather_features(x_d)
-                x = xg
-            else:
-                x = x_d
-            update(dy_d, x, w, m, v)
+            gathered_x = {g: all_gather_features(t) for g, t in x_by_grp.items()} if do_gather else x_by_grp
+            with K.UpdateGroup():
+                for (dy_d, _xd), i in zip(staged_in, members):
+                    name, V, H, grp, r0, r1, w, m, v = params[i]
+                    update(dy_d, gathered_x[grp], w, m, v)
             done = torch.cuda.Event()
             done.record(main)
-            for t in used:
-                last_use[t.data_ptr()] = done
+            for dy_d, xd in staged_in:
+                last_use[dy_d.data_ptr()] = done
+                last_use[xd.data_ptr()] = done
         # the step's result: the device status word and one updated weight, read back to the host
         host_result[0:1].copy_(_lib.status_word(dev)[0:1].float(), non_blocking=True)
         host_result[1:2].copy_(params[-1][6][0, 0:1].float(), non_blocking=True)
@@ -370,6 +384,102 @@ def run_forge(args):
         if sync:
             main.synchronize()
         return h2d, 8
+
+    # ---------------------------------------------------------------- the sharded mode's whole linear backward
+    # What a row-sharded layer really runs in its backward, per set of linears that share an input
+    # (q/k/v, o, gate/up, down, lm_head): the partial dX = sum_members dY_r W_r (library GEMM or
+    # forge_dgrad), its reduce-scatter over the ranks by NCCL on a communication stream, and the fused
+    # update of the members as one launch.  `regather` adds the all-gather of X for a design that keeps
+    # only activation shards between forward and backward.  At N = 1 the collectives vanish.
+    from forge_b200.autograd import _grad_input
+    from forge_b200.tensor_parallel import reduce_scatter_features
+    x_groups = []
+    for i, (name, V, H, grp, *_r) in enumerate(params):
+        if x_groups and x_groups[-1][0] == grp:
+            x_groups[-1][1].append(i)
+        else:
+            x_groups.append((grp, [i]))
+    tp_comm = torch.cuda.Stream()
+    dx_bufs = {}       # (H, slot) -> partial dX buffer; two per width so the next GEMM does not wait for the last scatter
+    dx_free = {}       # buffer -> event after the collective that last read it
+
+    def step_tp(step_no=None, parts=("dx", "rs", "update"), regather=False):
+        main = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(main)
+        tp_comm.wait_event(start)
+        dx_free.clear()
+        for gi, (grp, members) in enumerate(x_groups):
+            H = params[members[0]][2]
+            x = x_full[H]
+            if regather and world > 1:
+                with torch.cuda.stream(tp_comm):
+                    x = all_gather_features(x_shard[H])
+                    ev_x = torch.cuda.Event()
+                    ev_x.record(tp_comm)
+            key = (H, gi & 1)
+            if "dx" in parts or "rs" in parts:
+                if key not in dx_bufs:
+                    dx_bufs[key] = torch.empty(BT, H, dtype=torch.bfloat16, device=dev)
+                dx = dx_bufs[key]
+            if "dx" in parts:
+                ev = dx_free.get(key)
+                if ev is not None:
+                    main.wait_event(ev)
+                for k, i in enumerate(members):
+                    name, V, _H, _g, r0, r1, w, m, v = params[i]
+                    part = _grad_input(dys[r1 - r0], w)
+                    if k == 0:
+                        dx.copy_(part)
+                    else:
+                        dx.add_(part)
+            if "rs" in parts and world > 1:
+                ready = torch.cuda.Event()
+                ready.record(main)
+                tp_comm.wait_event(ready)
+                with torch.cuda.stream(tp_comm):
+                    reduce_scatter_features(dx)
+                    done = torch.cuda.Event()
+                    done.record(tp_comm)
+                dx_free[key] = done
+            if "update" in parts:
+                if regather and world > 1:
+                    main.wait_event(ev_x)
+                with K.UpdateGroup():
+                    for i in members:
+                        name, V, _H, _g, r0, r1, w, m, v = params[i]
+                        update(dys[r1 - r0], x, w, m, v)
+        end = torch.cuda.Event()
+        end.record(tp_comm)
+        main.wait_event(end)
+
+    def tp_parity_check():
+        """One row-sharded linear trained for two steps with the real NCCL all-gather and reduce-scatter,
+        per moment storage; the gathered weight must equal an unsharded FusedLinear's, bit for bit."""
+        from forge_b200 import FusedLinear
+        from forge_b200.tensor_parallel import RowShardedFusedLinear
+        out = {}
+        for mode in ("bf16", "int8", "fp8_block"):
+            g = torch.Generator().manual_seed(77)
+            bt, H, V = 128, 1024, 1288          # 161 groups of 8 rows: unequal shards at every world size
+            w0 = (torch.randn(V, H, generator=g) * 0.05).bfloat16()
+            tp = RowShardedFusedLinear.from_full_weight(w0.to(dev), optimizer_type="adamw", state_mode=mode).train()
+            full = FusedLinear(H, V, optimizer_type="adamw", state_mode=mode)
+            full.weight.data = w0.clone()
+            full = full.to(dev).to(torch.bfloat16).train()
+            c0, c1 = feature_range(H, rank, world)
+            for _ in range(2):
+                x = torch.randn(bt, H, generator=g).bfloat16()
+                gy = (torch.randn(bt, V, generator=g) * 1e-2).bfloat16()
+                tp.local.update_optimizer_config(lr=1e-2, weight_decay=0.01)
+                tp(x[:, c0:c1].to(dev).requires_grad_(True)).backward(gy[:, tp.row_start:tp.row_end].to(dev))
+                full.update_optimizer_config(lr=1e-2, weight_decay=0.01)
+                full(x.to(dev).requires_grad_(True)).backward(gy.to(dev))
+            gathered = tp.gather_full_weight()
+            nd = (gathered.view(torch.int16) != full.weight.detach().view(torch.int16)).sum().reshape(1)
+            dist.all_reduce(nd, op=dist.ReduceOp.MAX)
+            out[mode] = int(nd.item())
+        return out
 
     def barrier():
         if world > 1:
@@ -449,6 +559,26 @@ def run_forge(args):
                       after=(lambda: torch.cuda.current_stream().synchronize()) if g_e2e is not None else None)
     step_no += e2e_steps
     clocks = sampler.stop() if sampler else None
+
+    # the sharded mode's full linear backward (see step_tp), and what each part costs alone
+    tp_steps = max(1, min(args.steps, 5))
+    tp_ms = {}
+    if not args.no_tp_step:
+        variants = [("step", dict()), ("dx_gemm", dict(parts=("dx",))), ("update", dict(parts=("update",)))]
+        if world > 1:
+            variants += [("step_regather_x", dict(regather=True)), ("reduce_scatter", dict(parts=("rs",))),
+                         ("all_gather_x", dict(parts=(), regather=True))]
+        for label, kw in variants:
+            fn = (lambda kw: (lambda step_no=None: step_tp(step_no, **kw)))(kw)
+            set_step(step_no)
+            fn()
+            g_tp = capture(fn)
+            set_step(step_no)
+            g_tp.replay() if g_tp is not None else fn()
+            tp_ms[label], _ = timed(fn, tp_steps, step_no, graph=g_tp)
+            del g_tp
+        step_no += 1
+    parity = tp_parity_check() if world > 1 else None
     status = _lib.read_status(dev)
 
     peak_gb = torch.cuda.max_memory_allocated(dev) / 1e9
@@ -459,7 +589,7 @@ def run_forge(args):
 
     if rank == 0:
         peaks, peak_kind = measured_peaks()
-        launches = len(params)
+        launches = len(launches_idx)
         # algorithmic bytes this rank moves per step (row shard of the state, full X, dY slice)
         state_bytes = 6 if args.moments == "bf16" else 4 + 2 * 4 / 64   # per element: W + m + v (+ scales)
         alg = sum(algorithmic_bytes(r1 - r0, H, state_bytes=state_bytes) for _, V, H, _, r0, r1, *_ in params)
@@ -469,7 +599,8 @@ def run_forge(args):
             "metric": "fused_wgrad_adamw_ms_per_step", "value": ms_dev, "unit": "ms/step", "n_gpus": world,
             "steps": args.steps, "warmup": W, "ms_per_step": ms_dev, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "bt": BT, "linears": launches, "weights": "bf16", "moments": args.moments,
+            "config": {"workload": args.workload, "bt": BT, "linears": len(params), "launches_per_step": launches,
+                       "grouping": args.group, "weights": "bf16", "moments": args.moments,
                        "optimizer": "adamw", "launch": "cuda_graph" if g_dev is not None else "eager", "streams": n_streams,
                        "parallelism": (f"tp{world}-rows" + ("+gather-x" if do_gather else "")) if world > 1 else "single",
                        "l2": f"each weight and its moments are distinct buffers ({peak_gb:.0f} GB in total), so every launch "
@@ -487,6 +618,21 @@ def run_forge(args):
             "gpu_launches": launches * args.steps,
             "peak_hbm_gb": peak_gb, "device_status": status, "clocks": clocks,
         }
+        if tp_ms:
+            n_rs = len(x_groups)
+            act_full = sum(BT * params[m[0]][2] * 2 for _, m in x_groups)
+            line["tp_step"] = {
+                "what": "per set of linears sharing an input: partial dX GEMM, NCCL reduce-scatter of dX on a communication "
+                        "stream, fused update of the set as one launch; *_alone are the same parts timed by themselves",
+                "ms": tp_ms["step"], "dx_gemm_alone_ms": tp_ms["dx_gemm"], "update_alone_ms": tp_ms["update"],
+                "reduce_scatter_alone_ms": tp_ms.get("reduce_scatter"), "reduce_scatters_per_step": n_rs if world > 1 else 0,
+                "ms_regather_x": tp_ms.get("step_regather_x"), "all_gather_x_alone_ms": tp_ms.get("all_gather_x"),
+                "dx_gemm": "forge_dgrad" if __import__("forge_b200.autograd", fromlist=["x"]).use_forge_dgrad else "cuBLAS",
+                "saved_activation_bytes_per_rank": {"gathered_x": act_full, "x_shards": act_full // world},
+                "steps": tp_steps, "launch": "cuda_graph" if not args.eager else "eager"}
+        if parity is not None:
+            line["tp_parity"] = "bit-equal" if not any(parity.values()) else f"{sum(parity.values())} differ"
+            line["tp_parity_modes"] = parity
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args.workload)
         print(json.dumps(line))
@@ -546,12 +692,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--moments", default="bf16", choices=["bf16", "int8", "fp8_block"],
                     help="storage of the AdamW moments (int8 / fp8_block: codes + one fp32 absmax scale per row and 64 columns)")
+    ap.add_argument("--group", default="layer", choices=["layer", "x", "none"],
+                    help="weights per kernel launch: the projections of a decoder layer, the linears that share an input, or one")
     ap.add_argument("--streams", type=int, default=4, help="streams the independent updates of a step are spread over")
     ap.add_argument("--gather-x", action="store_true",
                     help="N > 1: all-gather the feature-sharded X by NCCL inside the timed step")
     ap.add_argument("--shard-of", type=int, default=1,
                     help="single-GPU diagnostic: give this GPU the row shard rank 0 would own in a job of this "
                          "many ranks (no communication), to time the kernels at shard sizes")
+    ap.add_argument("--no-tp-step", action="store_true", help="skip the tp_step record (dX GEMM + collectives + update)")
     ap.add_argument("--eager", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

