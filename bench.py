@@ -60,9 +60,9 @@ def workload_linears(name):
         lin = [(f"l{i}.{n}", V, H, f"l{i}.{g}") for i in range(LAYERS) for n, V, H, g in LAYER_LINEARS]
         lin.append(("lm_head", VOCAB, HIDDEN, "lm_head"))
         return lin
-    if name == "llama3.1-8b-layer":   # one decoder layer: the projection set of BASELINE configuration 1
+    if name == "llama3.1-8b-layer":   # one decoder layer: the seven projection shapes of Llama-3.1-8B
         return [(n, V, H, g) for n, V, H, g in LAYER_LINEARS]
-    if name == "qwen3-32b-linears":   # BASELINE configuration 4: 64 layers, hidden 5120, 64/8 heads of 128, FFN 25600
+    if name == "qwen3-32b-linears":   # Qwen3-32B: 64 layers, hidden 5120, 64/8 heads of 128, FFN 25600
         hid, qd, kv, ffn, vocab = 5120, 8192, 1024, 25600, 151936
         layer = [("q", qd, hid, "attn_in"), ("k", kv, hid, "attn_in"), ("v", kv, hid, "attn_in"), ("o", hid, qd, "attn_out"),
                  ("gate", ffn, hid, "mlp_in"), ("up", ffn, hid, "mlp_in"), ("down", hid, ffn, "mlp_out")]
@@ -173,7 +173,7 @@ def run_reference(args):
     value = sample_ms * scale
     desc = (f"one decoder layer (7 projections, {sum(V * H for _, V, H, _ in sample) / 1e6:.0f}M parameters), {steps} timed steps "
             f"at {sample_ms:.0f} ms each, scaled x{scale:.1f} by parameter count to the full workload")
-    print(json.dumps({
+    line = {
         "impl": "reference", "metric": "fused_wgrad_adamw_ms_per_step", "value": value, "unit": "ms/step",
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": value, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -182,7 +182,32 @@ def run_reference(args):
         "cpu_baseline": {"value": value, "unit": "ms/step", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": "ms/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-    }))
+    }
+    gpu = reference_gpu_kernel(scale)
+    if gpu is not None:
+        line["reference_gpu_kernel"] = gpu
+    print(json.dumps(line))
+
+
+def reference_gpu_kernel(scale):
+    """Beside the CPU figure: the reference's own default GPU kernel (Triton ``fused_grad_adamw``) timed on
+    this box's GPU over one decoder layer and scaled like the CPU sample -- the kernel this library is
+    written to beat.  Only where the installed reference (``baseline/_ref``) and a GPU are present; runs in
+    a process of its own (the reference shares its import name with this repository's alias package)."""
+    script = os.path.join(ROOT, "baseline", "reference_gpu_arm.py")
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref")) or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return None
+    try:
+        out = subprocess.run([sys.executable, script, "--steps", "10", "--warmup", "3"], capture_output=True, text=True,
+                             timeout=240)
+        rec = json.loads(out.stdout.strip().splitlines()[-1])
+    except Exception as e:  # noqa: BLE001 - the record is optional
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:120]}"}
+    if "layer_ms" in rec:
+        rec["value"] = rec["layer_ms"] * scale
+        rec["unit"] = "ms/step"
+        rec["sample"] = "one decoder layer's seven projections on the GPU, scaled by parameter count like the CPU sample"
+    return rec
 
 
 # ------------------------------------------------------------------------------------------------

@@ -1,4 +1,5 @@
-"""Whole-model training step with every ``nn.Linear`` fused (BASELINE configurations 2-4).
+"""Whole-model training step with every ``nn.Linear`` fused (Llama-3.1-8B with bf16 or int8 moments,
+Qwen3-32B with fp8 moments; batch 1 x 512 tokens).
 
 Builds a Llama-3.1-8B (or Qwen3-32B) architecture from its config with random weights -- no
 checkpoint, no dataset: tokens are uniform over the vocabulary -- swaps every ``nn.Linear`` for

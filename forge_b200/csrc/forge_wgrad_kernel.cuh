@@ -263,7 +263,11 @@ struct WgradCfg {
   static constexpr int kRoom = SMEM_BUDGET - kCtrlBytes - 1024 - kBaseStages * kOpStageBytes;
   // 64-column chunks when four such stages fit (always with one-byte codes, whose quantisation block
   // is 64 columns); otherwise 32-column chunks, which buy a deeper ring for the same bytes
+#ifdef FORGE_FORCE_CN32
+  static constexpr int kCN = (kSES == 1) ? 64 : 32;
+#else
   static constexpr int kCN = (kSES == 1 || 4 * state_stage_bytes(kWES, kSES, kNMom, 64) <= kRoom) ? 64 : 32;
+#endif
   static constexpr int kNumChunks = TILE_N / kCN;
   static constexpr int kWRB = kCN * kWES;                      // bytes per W row inside a chunk
   static constexpr int kSRB = (kNMom > 0) ? kCN * kSES : 0;    // bytes per moment row inside a chunk
@@ -271,14 +275,18 @@ struct WgradCfg {
   static constexpr int kSBytes = 128 * kSRB;
   static constexpr int kStageBytes = kWBytes + kNMom * kSBytes;
   static constexpr int kNSS_raw = kRoom / kStageBytes;
-  static constexpr int kNSS_cap = kNSS_raw >= 6 ? 6 : (kNSS_raw >= 4 ? 4 : 2);   // even, see the file comment
+  static constexpr int kNSS_cap = kNSS_raw >= 8 ? 8 : (kNSS_raw >= 6 ? 6 : (kNSS_raw >= 4 ? 4 : 2));   // even, see the file comment
   static constexpr int kNSS = kNSS_cap > FORGE_MAX_STATE_STAGES ? FORGE_MAX_STATE_STAGES : kNSS_cap;
   // Shared memory the state ring leaves over goes to operand stages (at most eight): with small
   // states (plain SGD, one moment) the kernel is bound by the panel loads, whose rate is the bytes
   // in flight over the L2 latency.
   static constexpr int kSpare = kRoom - kNSS * kStageBytes;
   static constexpr int kExtraStages = (kSpare / kOpStageBytes < 8 - kBaseStages) ? kSpare / kOpStageBytes : 8 - kBaseStages;
+#ifdef FORGE_NO_EXTRA_OP
+  static constexpr int kNStage = kBaseStages;
+#else
   static constexpr int kNStage = kBaseStages + (kExtraStages > 0 ? kExtraStages : 0);
+#endif
   static constexpr int kSmemBytes = kCtrlBytes + 1024 + kNStage * kOpStageBytes + kNSS * kStageBytes;
   static_assert(kNSS_raw >= 2, "two state stages must fit in shared memory");
   static_assert(kSES != 1 || kCN == 64, "one-byte codes need 64-column chunks (the quantisation block)");
@@ -289,9 +297,9 @@ constexpr int TQ_SLOTS = 4;
 struct alignas(16) CtrlBlock {
   uint64_t op_full[8];
   uint64_t op_empty[8];
-  uint64_t st_full[6];
-  uint64_t st_empty[6];
-  uint64_t st_done[6];
+  uint64_t st_full[8];
+  uint64_t st_empty[8];
+  uint64_t st_done[8];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint64_t tq_full[TQ_SLOTS];    // unit queue: filled by the scheduler (st.async, 4 bytes each)

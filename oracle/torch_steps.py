@@ -2,8 +2,8 @@
 
 Follows the reference's own pure-torch checkers: ``_reference_sgd_step`` and
 ``_reference_adamw_step`` (``tests/test_correctness.py:27-55``: materialise ``dY^T X``, then the
-textbook update with in-place torch ops) and its int8 quantiser (``:170-180``).  Also the baseline
-``BASELINE.json`` names for its first configuration: torch autograd + ``torch.optim.AdamW`` on CPU.
+textbook update with in-place torch ops) and its int8 quantiser (``:170-180``).  Also the plain
+baseline of the single-linear configuration: torch autograd + ``torch.optim.AdamW`` on CPU.
 Everything here runs on CPU tensors; it is the tolerance-level oracle and the timed CPU baseline.
 """
 

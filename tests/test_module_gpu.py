@@ -1,5 +1,5 @@
 """Module-level behaviour on the GPU: multi-step trajectories against torch autograd +
-``torch.optim.AdamW`` on the CPU (BASELINE configuration 0), gradient accumulation, the non-fused
+``torch.optim.AdamW`` on the CPU (one 1024 x 1024 linear, fp32 state, ten steps), gradient accumulation, the non-fused
 escape hatch, bias handling, checkpoint round trips, every optimizer / state mode under a manager."""
 
 import copy

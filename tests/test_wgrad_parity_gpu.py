@@ -69,7 +69,7 @@ def test_adamw_bf16_within_one_ulp(BT, V, H):
 
 
 def test_adamw_fp32_state_close():
-    """fp32 W/m/v (BASELINE configuration 0 layout): fp32 agreement up to summation order."""
+    """fp32 W/m/v (fp32 master weights and moments): fp32 agreement up to summation order."""
     BT, V, H = 512, 1024, 1024
     dy, x, w, m, v = gen_inputs(3, BT, V, H)
     dyb, xb = dy.bfloat16(), x.bfloat16()
