@@ -8,8 +8,10 @@ regular ``torch.optim.AdamW``, and reports the median step time and the peak dev
 
     python examples/llama_step.py --model llama3.1-8b --state bf16 --steps 20
     python examples/llama_step.py --model llama3.1-8b --baseline      # vanilla fused torch AdamW
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 examples/llama_step.py \
+        --model qwen3-32b --state fp8_block --tp 8                    # row-sharded over 8 GPUs (examples/tp_model.py)
 
-One JSON line on stdout.
+One JSON line on stdout (rank 0), with the SM clocks sampled while the timed steps ran.
 """
 
 import argparse
@@ -70,8 +72,15 @@ def main():
     ap.add_argument("--graph", action="store_true",
                     help="capture forward + backward (with the fused updates) + the small optimizer into one CUDA "
                          "graph and replay it; hyper-parameters reach the fused kernels through device memory")
+    ap.add_argument("--tp", type=int, default=0,
+                    help="row-sharded tensor parallelism over this many ranks (launch with torch.distributed.run); "
+                         "uses the decoder of examples/tp_model.py instead of the transformers model")
+    ap.add_argument("--no-group", action="store_true", help="one launch per linear instead of one per decoder layer")
     args = ap.parse_args()
+    if args.tp:
+        return run_tp(args)
 
+    from bench import ClockSampler
     from transformers import AutoModelForCausalLM
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -92,6 +101,8 @@ def main():
         autograd.use_forge_dgrad = args.forge_dgrad
         fused = swap_linears(model, args.state, args.forge_dgrad)
         manager = FusedOptimizerManager(model)
+        if not args.no_group:
+            manager.group_updates("layer")
         if args.graph:
             manager.enable_device_hyper(dev)
         opt = torch.optim.AdamW(manager.get_non_fused_params(), lr=1e-4, weight_decay=0.01, fused=True,
@@ -116,7 +127,10 @@ def main():
     if side is not None:
         side.wait_stream(torch.cuda.current_stream())
         torch.cuda.set_stream(side)
+    sampler = ClockSampler(0)
     for step in range(args.warmup + args.steps):
+        if step == args.warmup:
+            sampler.start()
         g = torch.Generator(device=dev).manual_seed(1000 + step)
         ids = torch.randint(0, cfg.vocab_size, (1, args.seq), device=dev, generator=g)
         if args.graph and graph is None and step == 2:
@@ -145,11 +159,13 @@ def main():
         if step >= args.warmup:
             times.append((time.perf_counter() - t0) * 1e3)
         losses.append(loss.item())
+    clocks = sampler.stop()
     status = 0
     if manager is not None:
         from forge_b200 import _lib
         status = _lib.read_status(dev)
     print(json.dumps({
+        "clocks": clocks, "grouped_launches": manager is not None and not args.no_group,
         "model": args.model, "layers": cfg.num_hidden_layers, "parameters": n_params, "seq": args.seq, "batch": 1,
         "impl": "torch AdamW(fused=True) baseline" if args.baseline else f"forge_b200 fused linears ({args.state} moments)",
         "fused_linears": fused, "median_ms_per_step": statistics.median(times), "min_ms": min(times), "max_ms": max(times),
@@ -157,6 +173,117 @@ def main():
         "first_loss": losses[0], "last_loss": losses[-1], "device_status": status,
         "forge_dgrad": bool(args.forge_dgrad), "cuda_graph": bool(args.graph), "data": "synthetic uniform tokens, random init",
     }))
+
+
+def run_tp(args):
+    """Whole-model step with every linear row-sharded over ``--tp`` ranks (one process per GPU)."""
+    import torch.distributed as dist
+    from bench import ClockSampler
+    from examples.tp_model import CONFIGS, TPDecoder
+    from forge_b200 import FusedOptimizerManager, _lib, autograd
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.tp:
+        raise SystemExit(f"--tp {args.tp} needs {args.tp} ranks (torch.distributed.run --nproc-per-node {args.tp}); got {world}")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    autograd.use_forge_dgrad = args.forge_dgrad
+    cfg = dict(CONFIGS[args.model])
+    if args.layers:
+        cfg["layers"] = args.layers
+    model = TPDecoder(cfg, state_mode=args.state, device=dev).train()
+    manager = FusedOptimizerManager(model)
+    if not args.no_group:
+        manager.group_updates("layer")
+    if args.graph:
+        manager.enable_device_hyper(dev)
+    opt = torch.optim.AdamW(manager.get_non_fused_params(), lr=1e-4, weight_decay=0.01, fused=True, capturable=args.graph)
+    head_norms = model.head_sharded_norm_params()
+    n_local = sum(p.numel() for p in model.parameters())
+    n_sharded = sum(m.weight.numel() for m in manager._fused_modules)
+    n_total = (n_local - n_sharded) + sum(m.in_features * m.out_features for m in model.modules()
+                                          if m.__class__.__name__ == "RowShardedFusedLinear")
+
+    def one_step(ids):
+        loss = model(ids)
+        loss.backward()
+        for p in head_norms:                      # per-head norm weights: sums over heads that live on other ranks
+            dist.all_reduce(p.grad)
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    static_ids = torch.zeros(1, args.seq, dtype=torch.long, device=dev)
+    static_loss = torch.zeros((), device=dev)
+    graph = None
+    side = torch.cuda.Stream() if args.graph else None
+    if side is not None:
+        side.wait_stream(torch.cuda.current_stream())
+        torch.cuda.set_stream(side)
+    torch.cuda.reset_peak_memory_stats(dev)
+    times, losses = [], []
+    sampler = ClockSampler(local) if rank == 0 else None
+    for step in range(args.warmup + args.steps):
+        if step == args.warmup and sampler:
+            sampler.start()
+        g = torch.Generator(device=dev).manual_seed(1000 + step)        # the same tokens on every rank
+        ids = torch.randint(0, cfg["vocab"], (1, args.seq), device=dev, generator=g)
+        if args.graph and graph is None and step == 2:
+            static_ids.copy_(ids)
+            manager.pre_step(lr=1e-4, weight_decay=0.01)
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    static_loss.copy_(one_step(static_ids).detach())
+                graph.replay()
+                torch.cuda.synchronize()
+                losses.append(static_loss.item())
+                continue
+            except Exception as e:  # pragma: no cover - depends on the NCCL build
+                sys.stderr.write(f"[tp] graph capture failed ({type(e).__name__}: {e}); eager steps\n")
+                graph, args.graph = None, False
+                torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        manager.pre_step(lr=1e-4, weight_decay=0.01)
+        if graph is not None:
+            static_ids.copy_(ids)
+            graph.replay()
+            loss = static_loss
+        else:
+            loss = one_step(ids)
+        e1.record()
+        torch.cuda.synchronize()
+        if step >= args.warmup:
+            times.append(e0.elapsed_time(e1))
+        losses.append(loss.item())
+    clocks = sampler.stop() if sampler else None
+    status = _lib.read_status(dev)
+    stats = torch.tensor([statistics.median(times), torch.cuda.max_memory_allocated(dev) / 1e9, float(status)], device=dev)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)            # slowest rank, largest footprint
+    if rank == 0:
+        ms = stats[0].item()
+        print(json.dumps({
+            "model": args.model, "layers": cfg["layers"], "parameters": n_total, "parameters_per_rank": n_local,
+            "seq": args.seq, "batch": 1, "tp": world,
+            "impl": f"forge_b200 row-sharded fused linears ({args.state} moments), NCCL all-gather / reduce-scatter",
+            "median_ms_per_step": ms, "tokens_per_s": args.seq / (ms * 1e-3), "steps": args.steps,
+            "peak_hbm_gb_per_rank": stats[1].item(), "first_loss": losses[0], "last_loss": losses[-1],
+            "device_status": int(stats[2].item()), "cuda_graph": bool(graph is not None),
+            "grouped_launches": not args.no_group, "forge_dgrad": bool(args.forge_dgrad), "clocks": clocks,
+            "timing": "CUDA events per step, median over steps, max over ranks",
+            "data": "synthetic uniform tokens (same on every rank), random init"}))
+    sys.stdout.flush()
+    del graph
+    torch.cuda.synchronize()
+    dist.barrier()
+    os._exit(0)
 
 
 if __name__ == "__main__":

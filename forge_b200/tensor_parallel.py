@@ -119,9 +119,14 @@ class RowShardedFusedLinear(nn.Module):
         self.in_features, self.out_features = in_features, out_features
         self.row_start, self.row_end = row_range(out_features, self.rank, self.world)
         self.gather_input = gather_input
-        self.local = FusedLinear(in_features, self.row_end - self.row_start, **fused_kwargs)
-        if dtype is not None or device is not None:
-            self.local = self.local.to(device=device, dtype=dtype)
+        # the shard is created where it will live: a large shard is never materialised on the host
+        if device is not None:
+            with torch.device(device):
+                self.local = FusedLinear(in_features, self.row_end - self.row_start, **fused_kwargs)
+        else:
+            self.local = FusedLinear(in_features, self.row_end - self.row_start, **fused_kwargs)
+        if dtype is not None:
+            self.local = self.local.to(dtype=dtype)
 
     @classmethod
     def from_full_weight(cls, weight: torch.Tensor, rank=None, world=None, group=None, **kw):
