@@ -103,7 +103,7 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
         dist.all_reduce(t, group=group)
         loss = (torch.log(s) + m - t).mean()
         p = e / s[:, None]
-        p[local, idx[local]] -= 1.0
+        p.scatter_add_(1, idx[:, None], -local.to(p.dtype)[:, None])      # minus one at the target, where it is local
         ctx.save_for_backward(p)
         ctx.dtype = logits_r.dtype
         return loss

@@ -86,6 +86,39 @@ class FusedLinearFunction(torch.autograd.Function):
         return grad_input, grad_weight, grad_bias, None, None, None, None, None, None
 
 
+def native_proto(weight, state):
+    """The argument block of one weight's fused update with everything that stays the same from step
+    to step filled in (W, moments, scales, dtypes, optimizer), for the C++ autograd node."""
+    from forge_b200 import _lib
+    w = weight.data
+    K._require_cuda(w)
+    K._row_major_2d(w, "weight")
+    opt = state.optimizer_type
+    if opt == "sgd":
+        st = K._state()
+    elif opt in ("sgdm", "lion"):
+        st = K._moment_state(state.m)
+    elif state.state_mode == "int8":
+        st = K._int8_state(w, state.m_q, state.v_q, state.m_scale, state.v_scale, state.qblock_size)
+    elif state.state_mode == "fp8_block":
+        st = K._int8_state(w, state.m_q, state.v_q, state.m_scale, state.v_scale, state.qblock_size, mode=_lib.ST_FP8_BLOCK)
+    elif state.state_mode == "fp8":
+        st = K._fp8_tensor_state(state)
+    else:
+        st = K._moment_state(state.m, state.v)
+    a = _lib.ForgeWgradArgs()
+    a.W = w.data_ptr()
+    a.V, a.H = w.shape
+    a.ld_w = w.stride(0)
+    a.operand_dtype = _lib.DT_BF16
+    a.w_dtype = _lib.dtype_id(w.dtype)
+    a.optimizer = _lib.OPTIMIZER_IDS[opt]
+    a.flags = 0
+    a.state = st
+    a.status = _lib.status_word(w.device).data_ptr()
+    return a
+
+
 class LayerUpdateGroup:
     """The fused updates of a fixed set of linears (the projections of a decoder layer, or q / k / v)
     issued as one launch.  Each member's backward records its update instead of launching it; when the
@@ -100,6 +133,13 @@ class LayerUpdateGroup:
         self._members = {w.data_ptr() for w in weights}
         self._seen: set[int] = set()
         self._group = K.UpdateGroup()
+        # the same set for members whose backward runs in the C++ autograd node
+        from forge_b200 import native
+        nat = native.module()
+        self.native = None
+        if nat is not None:
+            self.native = nat.Group()
+            self.native.set_members(sorted(self._members))
 
     def __len__(self):
         return len(self._members)
@@ -117,6 +157,8 @@ class LayerUpdateGroup:
     def flush(self):
         self._seen.clear()
         self._group.flush()
+        if self.native is not None:
+            self.native.flush()
 
 
 def _begin_update(state, config):

@@ -64,5 +64,37 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+TORCH_SRC = os.path.join(PKG, "csrc_torch", "forge_autograd.cpp")
+TORCH_EXT = os.path.join(PKG, "_forge_autograd.so")
+
+
+def build_torch_ext(force: bool = False, verbose: bool = False) -> str:
+    """Compile the C++ autograd node (``csrc_torch/forge_autograd.cpp``) against the installed PyTorch
+    into ``forge_b200/_forge_autograd.so`` (g++, no GPU needed).  It links against ``libforge_b200.so``
+    next to it, so ``build()`` must have run."""
+    import torch
+    from torch.utils import cpp_extension as C
+    hdr = os.path.join(ROOT, "include", "forge_b200.h")
+    if (not force and os.path.exists(TORCH_EXT)
+            and os.path.getmtime(TORCH_EXT) >= max(os.path.getmtime(TORCH_SRC), os.path.getmtime(hdr), os.path.getmtime(LIB))):
+        return TORCH_EXT
+    import sysconfig
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    inc = [*C.include_paths(), sysconfig.get_paths()["include"], os.path.join(cuda_home, "include")]
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=_forge_autograd",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           *[f"-I{i}" for i in inc], TORCH_SRC, "-o", TORCH_EXT,
+           *[f"-L{d}" for d in C.library_paths()], f"-L{PKG}", f"-L{os.path.join(cuda_home, 'lib64')}",
+           "-l:libforge_b200.so", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", "-ltorch_python", "-lcudart",
+           "-Wl,-rpath,$ORIGIN", *[f"-Wl,-rpath,{d}" for d in C.library_paths()]]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+    if r.returncode != 0:
+        raise RuntimeError("g++ failed: " + " ".join(cmd))
+    return TORCH_EXT
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_torch_ext(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -32,6 +32,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from forge_b200 import autograd as fa
+from forge_b200 import native
 from forge_b200.autograd import FusedLinearFunction, LayerUpdateGroup
 from forge_b200.state import FusedOptimizerState, OptimizerConfig
 
@@ -39,6 +41,8 @@ from forge_b200.state import FusedOptimizerState, OptimizerConfig
 class FusedLinear(nn.Module):
     """Drop-in ``nn.Linear`` whose backward computes the weight gradient tile by tile on chip and
     feeds it straight to the optimizer; the (out_features, in_features) gradient is never allocated."""
+
+    _native_dgrad = False    # the use_forge_dgrad switch as last told to the C++ autograd node
 
     def __init__(self, in_features, out_features, bias=False, optimizer_type="adamw",
                  quantize_state=False, state_mode=None, _adopt: nn.Linear | None = None,
@@ -71,6 +75,9 @@ class FusedLinear(nn.Module):
         self.use_fused_backward = True
         # set by FusedOptimizerManager.group_updates: the launch this module's update is issued with
         self._update_group = None
+        # handle of the C++ autograd node (forge_b200.native), created on first use
+        self._native = None
+        self._native_key = None
 
     @classmethod
     def from_linear(cls, linear: nn.Linear, optimizer_type="adamw", quantize_state=False,
@@ -101,10 +108,44 @@ class FusedLinear(nn.Module):
     def set_l2_manager(self, l2_manager):
         self._l2_manager = l2_manager
 
+    def _native_handle(self, nat):
+        """The C++ node's per-module handle, rebuilt whenever the weight or a state buffer moved."""
+        st = self._state
+        key = (self.weight.data_ptr(), st._version, self.weight.stride(0))
+        if self._native is None or self._native_key != key:
+            st.ensure_buffers()
+            key = (self.weight.data_ptr(), st._version, self.weight.stride(0))
+            from forge_b200.autograd import native_proto
+            h = self._native if self._native is not None else nat.Linear()
+            h.set_proto(bytes(native_proto(self.weight, st)))
+            if st._native is not h:
+                h.step = st.step
+                st._native = h
+            self._native, self._native_key = h, key
+        g = self._update_group
+        self._native.set_group(g.native if g is not None else None)
+        return self._native
+
     def forward(self, x):
         if not self.training:
             return F.linear(x, self.weight, self.bias)
         self._ensure_state()
+        cfg = self._config
+        if (cfg is not None and not self._is_accumulating and self.use_fused_backward and x.is_cuda
+                and x.dtype == torch.bfloat16 and self._state._pending_grad is None):
+            nat = native.module()
+            if nat is not None:
+                if cfg.optimizer_type != self._state.optimizer_type:
+                    raise ValueError(f"config asks for {cfg.optimizer_type!r} but the state was built for "
+                                     f"{self._state.optimizer_type!r}")
+                h = self._native_handle(nat)
+                hd = cfg.hyper_device
+                h.set_hyper(cfg.lr, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, cfg.momentum, bool(cfg.nesterov),
+                            hd.data_ptr() if hd is not None else 0)
+                if fa.use_forge_dgrad != FusedLinear._native_dgrad:
+                    nat.set_use_forge_dgrad(bool(fa.use_forge_dgrad))
+                    FusedLinear._native_dgrad = fa.use_forge_dgrad
+                return nat.fused_linear(x, self.weight, self.bias, h)
         return FusedLinearFunction.apply(x, self.weight, self.bias, self._state, self._config,
                                          self._is_accumulating, self._l2_manager,
                                          self.use_fused_backward, self._update_group)

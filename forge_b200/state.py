@@ -84,12 +84,25 @@ class FusedOptimizerState:
         self.state_mode = state_mode
         self.quantize_state = state_mode == "int8"
         self.qblock_size = qblock_size
-        self.step = 0
+        self._step = 0
+        self._native = None      # C++ autograd node's handle, which then owns the step count (see module.py)
+        self._version = 0        # bumped whenever a buffer is (re)allocated or replaced
         self._weight_ref = weight
         self._state_dtype = state_dtype if state_dtype is not None else weight.dtype
         self._pending_grad: Optional[torch.Tensor] = None
         for name in self._buffer_names():
             setattr(self, name, None)
+
+    @property
+    def step(self) -> int:
+        """Per-parameter count of updates (``state.py:159-160`` of the reference)."""
+        return self._native.step if self._native is not None else self._step
+
+    @step.setter
+    def step(self, value: int):
+        self._step = int(value)
+        if self._native is not None:
+            self._native.step = int(value)
 
     # ------------------------------------------------------------------ layout
     def _buffer_names(self):
@@ -112,6 +125,7 @@ class FusedOptimizerState:
         w = self._weight_ref
         V, H = w.shape
         dev = w.device
+        self._version += 1
         if self.optimizer_type in _ONE_MOMENT:
             self.m = torch.zeros(V, H, dtype=self._state_dtype, device=dev)
         elif self.state_mode == "bf16":
@@ -181,6 +195,7 @@ class FusedOptimizerState:
             if has_buffers:
                 raise ValueError(f"checkpoint holds {mode!r} state but this parameter uses {self.state_mode!r}")
         self.step = d["step"]
+        self._version += 1
         for name in self._buffer_names():
             if name in d:
                 setattr(self, name, d[name].clone().to(self._weight_ref.device))

@@ -29,6 +29,8 @@ def test_reference_arm_line():
     assert out.returncode == 0, out.stderr
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["unit"] == "ms/step" and line["higher_is_better"] is False
-    assert line["cpu_baseline"]["kind"] == "reference" and line["cpu_baseline"]["cores"] >= 1
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["value"] > 0
     assert line["metric"] == "fused_wgrad_adamw_ms_per_step"
+    # no GPU here: the reference's GPU kernel is either reported as unavailable or left out
+    assert "layer_ms" not in line.get("reference_gpu_kernel", {})
