@@ -12,3 +12,5 @@ from forge_b200.state import FusedOptimizerState, OptimizerConfig
 
 __version__ = "0.1.0"
 __all__ = ["FusedLinear", "FusedOptimizerManager", "OptimizerConfig", "FusedOptimizerState"]
+# also here: forge_b200.rmsnorm_linear (FusedRMSNormLinear, fuse_rmsnorm_linear_pairs), forge_b200.tensor_parallel,
+# forge_b200.kernel (operator wrappers, UpdateGroup)

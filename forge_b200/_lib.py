@@ -116,6 +116,10 @@ _SIGNATURES = {
     "forge_optimizer_update": (ctypes.c_int, [ctypes.POINTER(ForgeOptimArgs), ctypes.c_void_p]),
     "forge_fp8_prestep": (ctypes.c_int, [ctypes.c_void_p] * 5),
     "forge_dgrad": (ctypes.c_int, [ctypes.c_void_p] * 3 + [ctypes.c_int64] * 6 + [ctypes.c_void_p] * 2),
+    "forge_rmsnorm_forward": (ctypes.c_int, [ctypes.c_void_p] * 3 + [ctypes.c_int64] * 4 + [ctypes.c_double, ctypes.c_void_p]),
+    "forge_rmsnorm_backward": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int32] * 2 + [ctypes.c_int64] * 5
+                               + [ctypes.c_double, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "forge_rmsnorm_backward_scratch_bytes": (ctypes.c_size_t, [ctypes.c_int64, ctypes.c_int64]),
     "forge_state_bytes": (
         ctypes.c_int,
         [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,

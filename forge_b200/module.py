@@ -211,6 +211,10 @@ class FusedOptimizerManager:
             lr = 1e-4
         for g in self._update_groups:      # nothing recorded in an earlier pass may wait any longer
             g.flush()
+        for m in self._fused_modules:      # norms shared by sibling linears: forget passes that never finished
+            shared = getattr(m, "_shared", None)
+            if shared is not None:
+                shared.reset()
         # one shared config per distinct (optimizer, constructor keywords, device) instead of one per module
         configs: dict[tuple, OptimizerConfig] = {}
         for m in self._fused_modules:

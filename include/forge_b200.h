@@ -198,6 +198,24 @@ int forge_fp8_prestep(float* m_scale, float* v_scale, float* m_absmax_next, floa
 int forge_dgrad(const void* dY, const void* W, void* dX, int64_t BT, int64_t V, int64_t H,
                 int64_t ld_dy, int64_t ld_w, int64_t ld_dx, int32_t* status, void* cuda_stream);
 
+/* RMSNorm recomputation for linears that fold their preceding norm (the normalised activation is not
+ * kept between forward and backward): y = bf16(gamma * (x * rsqrt(mean(x^2) + eps))), fp32 inside;
+ * x, gamma, y bf16; x and y (rows, H) row-major, H a multiple of 8 and at most 16384.  Replaces
+ * _rmsnorm_forward (src/fused_grad_optimizer/fused_rmsnorm_linear.py:32-41). */
+int forge_rmsnorm_forward(const void* x, const void* gamma, void* y, int64_t rows, int64_t H, int64_t ld_x,
+                          int64_t ld_y, double eps, void* cuda_stream);
+
+/* Backward of the same norm: grad_x = g gamma rrms - x (sum_h g gamma x) rrms^3 / H (bf16) and
+ * grad_gamma = sum_rows g x rrms, written (accumulate = 0) or added (accumulate = 1) to grad_gamma of
+ * type grad_gamma_dtype (FORGE_DT_BF16 or FORGE_DT_F32).  The column sums are reduced in two
+ * fixed-order stages through `scratch` (forge_rmsnorm_backward_scratch_bytes), so results are
+ * bit-reproducible.  Replaces _rmsnorm_backward (fused_rmsnorm_linear.py:44-62). */
+int forge_rmsnorm_backward(const void* x, const void* gamma, const void* grad_y, void* grad_x, void* grad_gamma,
+                           int32_t grad_gamma_dtype, int32_t accumulate, int64_t rows, int64_t H, int64_t ld_x,
+                           int64_t ld_gy, int64_t ld_gx, double eps, void* scratch, size_t scratch_bytes,
+                           void* cuda_stream);
+size_t forge_rmsnorm_backward_scratch_bytes(int64_t rows, int64_t H);
+
 /* Bytes of optimizer state the allocator must provide for a (V, H) parameter: the moment arrays
  * and, separately, the scale arrays (src/fused_grad_optimizer/state.py:95-130). */
 int forge_state_bytes(int32_t optimizer, int32_t mode, int64_t V, int64_t H, int32_t qblock,
