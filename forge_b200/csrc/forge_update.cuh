@@ -122,8 +122,9 @@ __device__ __forceinline__ float2 adamw_update2(float2 w, float2 g, float2& m, f
   const float2 b1 = make_float2(h.beta1, h.beta1), c1 = make_float2(h.one_m_beta1, h.one_m_beta1);
   const float2 b2 = make_float2(h.beta2, h.beta2), c2 = make_float2(h.one_m_beta2, h.one_m_beta2);
   // The products are packed; the sums are scalar adds.  A packed add fed by a packed multiply came
-  // out of the assembler as one fused operation (m', v' off by an ulp in 5 % of the elements), and
-  // the moments must match the separately rounded reference arithmetic bit for bit.
+  // out of the assembler as one fused operation (m', v' off by an ulp in 5 % of the elements), and so
+  // did a packed multiply-add with the multiplier one standing in for the add; the moments must
+  // match the separately rounded reference arithmetic bit for bit.
   const float2 pm = fmul2(b1, m), pg = fmul2(c1, g);
   m = make_float2(f_add(pm.x, pg.x), f_add(pm.y, pg.y));
   const float2 pv = fmul2(b2, v), pgg = fmul2(fmul2(c2, g), g);
@@ -187,6 +188,13 @@ __device__ __forceinline__ uint32_t int8_code_bits(float x, float scale, float r
   asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(div_by_rcp(x, scale, rscale)));
   return static_cast<uint32_t>(q) & 0xFFu;
 }
+// max(a, b, c) in one instruction (three-input form of sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // ---- the same quantiser arithmetic on element pairs, without the conversion unit ----------------
 // Correctly rounded a / b on two elements given neg_b = -b and rb = RN(1 / b) (div_by_rcp, packed).
 __device__ __forceinline__ float2 div2_by_rcp(float2 a, float2 neg_b, float2 rb) {
@@ -201,6 +209,13 @@ __device__ __forceinline__ float2 int8x2_to_float(uint32_t biased, int first) {
   const float f0 = __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7540u + first));
   const float f1 = __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7541u + first));
   return fadd2(make_float2(f0, f1), make_float2(-8388736.0f, -8388736.0f));
+}
+// Two NON-NEGATIVE int8 codes (second moments: 0..127) -> fp32, exactly; no sign-bit flip needed: the
+// byte itself dropped into the mantissa of 2^23 reads as 2^23 + code.
+__device__ __forceinline__ float2 uint8x2_to_float(uint32_t codes, int first) {
+  const float f0 = __uint_as_float(__byte_perm(codes, 0x4B000000u, 0x7540u + first));
+  const float f1 = __uint_as_float(__byte_perm(codes, 0x4B000000u, 0x7541u + first));
+  return fadd2(make_float2(f0, f1), make_float2(-8388608.0f, -8388608.0f));
 }
 // rint() of two quotients as the low bytes of q + 1.5 * 2^23 (round to nearest even; two's
 // complement in the mantissa).  |q| < 127.5 by construction of the scale, so no clamp is needed.

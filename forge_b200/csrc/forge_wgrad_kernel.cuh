@@ -766,19 +766,23 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
         const int s = q % NSS;
         const uint32_t ph = (q / NSS) & 1;
 
-        // accumulator row: the CN fp32 columns of this chunk
-        uint32_t acc[CN];
-        {
-          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                 static_cast<uint32_t>(buf * TILE_N + c * CN);
-          tmem_ld_32x32(taddr, &acc[0]);
-          if constexpr (CN == 64) tmem_ld_32x32(taddr + 32, &acc[32]);
+        // accumulator row: the CN fp32 columns of this chunk.  The block-quantised modes fetch it in
+        // groups of 16 columns as they go (they keep 64 new second moments in registers already)
+        constexpr bool kTmemScratch = (ST == ST_INT8 || ST == ST_FP8_BLOCK);
+        constexpr int ACC_REGS = kTmemScratch ? 16 : CN;
+        uint32_t acc[ACC_REGS];
+        const uint32_t acc_taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(buf * TILE_N + c * CN);
+        if constexpr (kTmemScratch) {
+          tmem_ld_32x16(acc_taddr, &acc[0]);
+        } else {
+          tmem_ld_32x32(acc_taddr, &acc[0]);
+          if constexpr (CN == 64) tmem_ld_32x32(acc_taddr + 32, &acc[32]);
         }
         ok = mbar_wait(&ctrl->st_full[s], ph, abort_word, ERR_WAIT_ST_FULL);
         ok = __all_sync(0xffffffffu, ok);
         tmem_ld_wait();
         if (!ok) break;
-        constexpr bool kTmemScratch = (ST == ST_INT8 || ST == ST_FP8_BLOCK);
         if (!kTmemScratch && i == half_chunks - 1) {
           // this warp's last read of the accumulator: hand the buffer back to the MMA issuer now,
           // not after the update of the chunk
@@ -789,9 +793,10 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
             else mbar_arrive(&ctrl->acc_empty[buf]);
           }
         }
-        if (pp->num_kb == 0) {
+        const bool no_tokens = pp->num_kb == 0;
+        if (no_tokens) {
 #pragma unroll
-          for (int k = 0; k < CN; ++k) acc[k] = 0u;
+          for (int k = 0; k < ACC_REGS; ++k) acc[k] = 0u;
         }
 
         uint8_t* wb = st_buf + s * Cfg::kStageBytes;
@@ -876,27 +881,30 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
           const float sm_old = (i == 0) ? sc_m[0] : sc_m[1];
           const float sv_old = (i == 0) ? sc_v[0] : sc_v[1];
           const float2 sm_old2 = make_float2(sm_old, sm_old), sv_old2 = make_float2(sv_old, sv_old);
-          const uint32_t scratch = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(buf * TILE_N + c * CN);
+          const uint32_t scratch = acc_taddr;
           float vv[CN];
           float am = 0.0f, av = 0.0f;
 #pragma unroll
           for (int g = 0; g < NG; ++g) {
             float w[16];
-            uint32_t mq[4], vq[4], mnew[16];
+            uint32_t mq[4], vq[4], mnew[16], acc_next[16];
+            // the accumulator columns of the next group are on their way while this one is worked on
+            if (g + 1 < NG) tmem_ld_32x16(acc_taddr + 16 * (g + 1), acc_next);
             unpack16<WES>(load_raw<WES, WRB>(wb, r, g), w);
             ld16_bytes(mb, r, g, mq);
             ld16_bytes(vb, r, g, vq);
             if constexpr (ST == ST_INT8) {
+              // first moments are signed: flip the sign bits so that a byte reads as code + 128; second
+              // moments are never negative and are taken as they are
 #pragma unroll
-              for (int j = 0; j < 4; ++j) { mq[j] ^= 0x80808080u; vq[j] ^= 0x80808080u; }
+              for (int j = 0; j < 4; ++j) mq[j] ^= 0x80808080u;
             }
 #pragma unroll
             for (int k = 0; k < 16; k += 2) {
               float2 m2, v2;
               if constexpr (ST == ST_INT8) {
                 m2 = int8x2_to_float(mq[k >> 2], k & 3);
-                v2 = int8x2_to_float(vq[k >> 2], k & 3);
+                v2 = uint8x2_to_float(vq[k >> 2], k & 3);
               } else {
                 e4m3x2_to_float(mq[k >> 2] >> (8 * (k & 3)), m2.x, m2.y);
                 e4m3x2_to_float(vq[k >> 2] >> (8 * (k & 3)), v2.x, v2.y);
@@ -906,7 +914,7 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
               v2.x = fmaxf(v2.x, 1e-8f);
               v2.y = fmaxf(v2.y, 1e-8f);
               const float2 w2 = adamw_update2(make_float2(w[k], w[k + 1]),
-                                              make_float2(__uint_as_float(acc[16 * g + k]), __uint_as_float(acc[16 * g + k + 1])),
+                                              make_float2(__uint_as_float(acc[k]), __uint_as_float(acc[k + 1])),
                                               m2, v2, hy);
               w[k] = w2.x;
               w[k + 1] = w2.y;
@@ -914,11 +922,16 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
               mnew[k + 1] = __float_as_uint(m2.y);
               vv[16 * g + k] = v2.x;
               vv[16 * g + k + 1] = v2.y;
-              am = fmaxf(am, fmaxf(fabsf(m2.x), fabsf(m2.y)));
-              av = fmaxf(av, fmaxf(fabsf(v2.x), fabsf(v2.y)));
+              am = fmax3(am, fabsf(m2.x), fabsf(m2.y));
+              av = fmax3(av, v2.x, v2.y);          // second moments are sums of non-negative terms
             }
             tmem_st_32x16(scratch + 16 * g, mnew);
             store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
+            if (g + 1 < NG) {
+              tmem_ld_wait();
+#pragma unroll
+              for (int k = 0; k < 16; ++k) acc[k] = no_tokens ? 0u : acc_next[k];
+            }
           }
           tmem_st_wait();
           const float sm_new = (ST == ST_INT8) ? int8_scale(am) : fp8blk_scale(am);
