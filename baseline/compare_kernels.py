@@ -14,8 +14,10 @@ Arms (each skipped with a note if it cannot be loaded):
 
 The reference is imported from ``baseline/_ref`` (``pip install --target baseline/_ref <reference>``),
 which must come first on ``sys.path`` because this repository ships an alias package of the same
-import name.  Timing: CUDA events, median of 30, a 256 MB buffer written between iterations to flush L2.
-One JSON object per shape on stdout.
+import name.  Timing: CUDA events, median of 30, a 256 MB buffer written between iterations to flush L2;
+every row carries the SM clocks sampled while it was timed (``time x median MHz`` compares runs taken
+at different clocks).  One JSON object per shape on stdout, then ``--steps N`` (default 50) free-running
+steps with int8 moments against the reference's own int8 kernel from the same fresh state.
 """
 
 import json
@@ -90,11 +92,67 @@ def load_arms():
     return arms, notes
 
 
-def main():
+def int8_trajectory(steps):
+    """``steps`` training steps with int8 moments, fresh Gaussian dY / X per step, from the reference's
+    initial state (codes 0, scales 1): this library and the reference's Triton int8 kernel
+    (``kernel.py:1487-1539``) side by side, no resynchronisation; agreement of W, codes and scales at
+    the end (the Llama-3.1-8B int8 configuration asks for it over 50 steps)."""
     dev = "cuda"
+    from forge_b200 import kernel as FK
+    try:
+        import fused_grad_optimizer.kernel as RK
+        assert "_ref" in RK.__file__, RK.__file__
+    except Exception as e:  # pragma: no cover
+        print(json.dumps({"int8_trajectory": "unavailable", "why": f"{type(e).__name__}: {e}"}), flush=True)
+        return
+    for name, V, H in (("k/v", 1024, 4096), ("q/o", 4096, 4096)):
+        g0 = torch.Generator(device=dev).manual_seed(3)
+        w0 = (torch.randn(V, H, device=dev, generator=g0) * 0.02).bfloat16()
+
+        def fresh():
+            return (w0.clone(), torch.zeros(V, H, dtype=torch.int8, device=dev), torch.zeros(V, H, dtype=torch.int8, device=dev),
+                    torch.ones(V, H // 64, device=dev), torch.ones(V, H // 64, device=dev))
+        a, b = fresh(), fresh()
+        for step in range(1, steps + 1):
+            g = torch.Generator(device=dev).manual_seed(1000 + step)
+            x = torch.randn(BT, H, device=dev, generator=g).bfloat16()
+            dy = (torch.randn(BT, V, device=dev, generator=g) * 1e-2).bfloat16()
+            FK.fused_grad_adamw_int8state(dy, x, *a, step=step, **HYPER)
+            RK.fused_grad_adamw_int8state(dy, x, *b, step=step, **HYPER)
+        torch.cuda.synchronize()
+        row = {"int8_trajectory": name, "V": V, "H": H, "BT": BT, "steps": steps}
+        dw = (a[0].float() - b[0].float()).abs()
+        ulp = torch.pow(2.0, torch.floor(torch.log2(torch.maximum(a[0].float().abs(), b[0].float().abs()).clamp_min(2.0 ** -126))) - 7)
+        row["W_max_abs_diff"] = float(dw.max())
+        row["W_frac_beyond_one_bf16_ulp"] = float((dw > ulp).float().mean())
+        for nm, i in (("m", 1), ("v", 2)):
+            d = (a[i].int() - b[i].int()).abs()
+            row[nm + "_codes_equal_frac"] = float((d == 0).float().mean())
+            row[nm + "_codes_max_diff"] = int(d.max())
+        row["m_scale_max_rel"] = float(((a[3] - b[3]).abs() / b[3].abs()).max())
+        row["v_scale_max_rel"] = float(((a[4] - b[4]).abs() / b[4].abs()).max())
+        row["note"] = ("the reference's kernel evaluates the update with Triton's approximate division / square root and "
+                       "fused multiply-adds; this library rounds every moment operation separately (as the reference's "
+                       "torch checker does) -- the codes differ where a quotient lands within that noise of .5")
+        print(json.dumps(row), flush=True)
+
+
+def main():
+    import argparse
+    from bench import ClockSampler
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=50, help="free-running int8 steps against the reference's int8 kernel (0: skip)")
+    ap.add_argument("--no-timing", action="store_true", help="only the int8 trajectory")
+    args = ap.parse_args()
+    dev = "cuda"
+    if args.no_timing:
+        int8_trajectory(args.steps)
+        return
     arms, notes = load_arms()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for name, V, H in SHAPES:
+        sampler = ClockSampler(torch.cuda.current_device())
+        sampler.start()
         g = torch.Generator(device=dev).manual_seed(0)
         dy = (torch.randn(BT, V, device=dev, generator=g) * 1e-2).bfloat16()
         x = torch.randn(BT, H, device=dev, generator=g).bfloat16()
@@ -125,8 +183,11 @@ def main():
                 row[arm + "_max_rel_dm_vs_forge"] = float(((m1.float() - ref_w[1]).abs() / (ref_w[1].abs() + 1e-6)).max())
         for k, vnote in notes.items():
             row[k + "_unavailable"] = vnote
+        row["clocks"] = sampler.stop()
         print(json.dumps(row), flush=True)
         int8_row(name, V, H, dy, x, flush)
+    if args.steps > 0:
+        int8_trajectory(args.steps)
 
 
 def int8_row(name, V, H, dy, x, flush):

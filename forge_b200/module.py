@@ -87,8 +87,25 @@ class FusedLinear(nn.Module):
                    optimizer_type=optimizer_type, quantize_state=quantize_state,
                    state_mode=state_mode, _adopt=linear, **optimizer_kwargs)
 
+    def _check_shape(self):
+        """The kernels move rows with the copy engine, which needs 16-byte row pitches: say so here, at the
+        first training forward, not from inside a backward pass (the reference masks ragged shapes in
+        its Triton kernels, ``kernel.py:261-265``)."""
+        per16 = 16 // self.weight.element_size()
+        if self.in_features % per16 or self.out_features % 8:
+            raise ValueError(
+                f"FusedLinear({self.in_features}, {self.out_features}) with {self.weight.dtype} weights: in_features must be a "
+                f"multiple of {per16} and out_features a multiple of 8 (16-byte rows of W, X and dY); pad the layer or keep it "
+                f"a plain nn.Linear")
+        if self.state_mode in ("int8", "fp8_block") and self.in_features % 64:
+            raise ValueError(f"state_mode={self.state_mode!r} needs in_features ({self.in_features}) divisible by 64, the "
+                             f"quantisation block (as in the reference, kernel.py:1513)")
+        if self.state_mode == "fp8" and self.in_features % 16:
+            raise ValueError(f"state_mode='fp8' needs in_features ({self.in_features}) divisible by 16")
+
     def _ensure_state(self):
         if self._state is None:
+            self._check_shape()
             self._state = FusedOptimizerState(self.weight, self.optimizer_type,
                                               quantize_state=self.quantize_state,
                                               state_mode=self.state_mode)

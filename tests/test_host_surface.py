@@ -204,3 +204,47 @@ def test_alias_package():
     from fused_grad_optimizer.module import FusedLinear as FL, FusedOptimizerManager as FM  # noqa: F401
     from fused_grad_optimizer.state import FusedOptimizerState as FS, OptimizerConfig as OC  # noqa: F401
     assert fused_grad_optimizer.FusedLinear is FusedLinear and FL is FusedLinear
+
+
+def test_unsupported_shapes_are_refused_at_the_first_forward():
+    """Row pitches the copy engine cannot take raise a clear ValueError before any kernel is involved."""
+    lin = FusedLinear(100, 64).train()                     # fp32 weights: in_features % 4 is fine ...
+    lin = lin.bfloat16()                                   # ... bf16 needs in_features % 8
+    with pytest.raises(ValueError, match="multiple of 8"):
+        lin(torch.zeros(4, 100, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="divisible by 64"):
+        FusedLinear(96, 64, state_mode="int8").train()(torch.zeros(4, 96))
+    FusedLinear(96, 64).eval()(torch.zeros(4, 96))          # eval mode is a plain linear: anything goes
+
+
+def test_layer_groups_are_formed_by_name_prefix():
+    """``group_updates("layer")``: modules under the same numbered block share a launch, largest weights
+    first, at most eight per group; modules outside numbered blocks stay on their own."""
+    import torch.nn as nn
+
+    class Blk(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.attn = nn.ModuleDict({n: FusedLinear(64, o) for n, o in (("q", 64), ("k", 16), ("v", 16), ("o", 64))})
+            self.mlp = nn.ModuleDict({"gate": FusedLinear(64, 128), "up": FusedLinear(64, 128), "down": FusedLinear(128, 64)})
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleList([Blk(), Blk()])
+            self.lm_head = FusedLinear(64, 256)
+
+    net = Net()
+    mgr = FusedOptimizerManager(net).group_updates("layer")
+    assert len(mgr._update_groups) == 2 and all(len(g) == 7 for g in mgr._update_groups)
+    assert net.lm_head._update_group is None
+    assert net.layers[0].attn["q"]._update_group is net.layers[0].mlp["down"]._update_group
+    assert net.layers[0].attn["q"]._update_group is not net.layers[1].attn["q"]._update_group
+    mgr.group_updates([[net.layers[0].attn["q"], net.layers[0].attn["k"]]])      # regrouping replaces the old groups
+    assert len(mgr._update_groups) == 1 and net.layers[1].attn["q"]._update_group is None
+    with pytest.raises(ValueError):
+        mgr.group_updates([[net.lm_head, FusedLinear(8, 8)]])                     # not a module of this model
+    mixed = Net()
+    mixed.layers[0].attn["k"] = FusedLinear(64, 16, state_mode="int8")
+    g = FusedOptimizerManager(mixed).group_updates("layer")._update_groups
+    assert sorted(len(x) for x in g) == [6, 7]          # the int8 module cannot share a launch with bf16 ones
