@@ -254,7 +254,8 @@ def run_forge(args):
     else:
         keyed: dict[str, list[int]] = {}
         for i, (name, V, H, grp, *_r) in enumerate(params):
-            key = grp if args.group == "x" else (name.split(".")[0] if "." in name else name)
+            # "l17.q" -> decoder layer 17; the one-layer workload's bare names form one layer; lm_head stands alone
+            key = grp if args.group == "x" else (name.split(".")[0] if "." in name else ("layer" if name != "lm_head" else name))
             keyed.setdefault(key, []).append(i)
         # largest weights first inside a launch: the small ones fill the ragged end
         launches_idx = [sorted(ix, key=lambda i: -(params[i][5] - params[i][4]) * params[i][2]) for ix in keyed.values()]
