@@ -638,7 +638,8 @@ def run_forge(args):
                          "algorithmic_bytes_per_launch": alg / launches, "avg_launch_us": ms_dev * 1e3 / launches,
                          "tflops": flops / (ms_dev * 1e-3) / 1e12,
                          # dram read+write per launch from the ncu capture in profiles/, scaled by bytes
-                         "traffic": TRAFFIC_RATIO * alg / launches if (TRAFFIC_RATIO and args.moments == "bf16") else None},
+                         "traffic": TRAFFIC_RATIO * alg / launches if (TRAFFIC_RATIO and args.moments == "bf16") else None,
+                         "traffic_source": "ncu capture of one grouped decoder-layer launch (profiles/), scaled by algorithmic bytes"},
             "e2e": {"value": ms_e2e, "unit": "ms/step", "h2d_bytes_per_step": moved[0], "d2h_bytes_per_step": moved[1],
                     "steps": e2e_steps},
             "gpu_launches": launches * args.steps,
@@ -673,10 +674,11 @@ def run_forge(args):
         os._exit(0)
 
 
-# dram bytes (read + write) inside the launches per algorithmic byte, from the ncu capture summarised
-# in profiles/wgrad_adamw_bf16_llama8b_layer_ncu.md (reads equal the algorithmic reads; the writes still
-# dirty in L2 when a launch ends make the in-launch total smaller than the algorithmic one)
-TRAFFIC_RATIO = 0.88
+# dram bytes (read + write) inside the launches per algorithmic byte, from the ncu capture of one grouped
+# decoder-layer launch summarised in profiles/wgrad_adamw_layer_group_llama8b_ncu.md (reads are slightly
+# below the algorithmic reads because linears of a group share X in L2; the writes still dirty in L2
+# when a launch ends make the in-launch total smaller than the algorithmic one)
+TRAFFIC_RATIO = 0.97
 
 
 def cpu_baseline(workload):
