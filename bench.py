@@ -7,8 +7,8 @@ reference fuses -- 32 decoder layers x (q 4096x4096, k 1024x4096, v 1024x4096, o
 gate 14336x4096, up 14336x4096, down 4096x14336) plus lm_head 128256x4096 -- at BT = 512 tokens,
 bf16 weights and bf16 AdamW moments, random-initialised, synthetic activations X ~ N(0,1) and
 gradients dY ~ N(0, 1e-2) in bf16.  A *step* is one fused wgrad+AdamW update of each of the 225
-weights.  ``--group layer`` (default) issues the seven projections of a decoder layer as ONE kernel
-launch (``forge_wgrad_update_group``: 33 launches per step), ``--group x`` one launch per set of
+weights.  ``--group layer`` (default) issues the projections of two decoder layers (14 weights) as ONE
+kernel launch (``forge_wgrad_update_group``: 17 launches per step; ``--layers-per-launch 1``: 33), ``--group x`` one launch per set of
 linears that share their input (q/k/v, gate/up), ``--group none`` one launch per weight as the
 reference does.  Every weight and its moments are distinct buffers (45 GB in total), so each launch
 streams cold state; only the small X / dY panels may sit in L2, as they do in training where the
@@ -249,13 +249,21 @@ def run_forge(args):
         params.append((name, V, H, grp, r0, r1, w, m, v))
 
     # launches: lists of indices into `params` whose updates are issued together
+    # decoder layers per launch: two (14 weights; the fixed cost of a launch is paid half as often, which is
+    # worth 2 % on one GPU and 4 % at the shard sizes of eight ranks)
+    lpl = min(2, args.layers_per_launch) if args.layers_per_launch > 0 else 2
     if args.group == "none":
         launches_idx = [[i] for i in range(len(params))]
     else:
         keyed: dict[str, list[int]] = {}
         for i, (name, V, H, grp, *_r) in enumerate(params):
             # "l17.q" -> decoder layer 17; the one-layer workload's bare names form one layer; lm_head stands alone
-            key = grp if args.group == "x" else (name.split(".")[0] if "." in name else ("layer" if name != "lm_head" else name))
+            if args.group == "x":
+                key = grp
+            elif "." in name:
+                key = "l%d" % (int(name.split(".")[0][1:]) // lpl)
+            else:
+                key = "layer" if name != "lm_head" else name
             keyed.setdefault(key, []).append(i)
         # largest weights first inside a launch: the small ones fill the ragged end
         launches_idx = [sorted(ix, key=lambda i: -(params[i][5] - params[i][4]) * params[i][2]) for ix in keyed.values()]
@@ -626,7 +634,7 @@ def run_forge(args):
             "steps": args.steps, "warmup": W, "ms_per_step": ms_dev, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "bt": BT, "linears": len(params), "launches_per_step": launches,
-                       "grouping": args.group, "weights": "bf16", "moments": args.moments,
+                       "grouping": args.group + (f" x{lpl}" if args.group == "layer" and lpl > 1 else ""), "weights": "bf16", "moments": args.moments,
                        "optimizer": "adamw", "launch": "cuda_graph" if g_dev is not None else "eager", "streams": n_streams,
                        "parallelism": (f"tp{world}-rows" + ("+gather-x" if do_gather else "")) if world > 1 else "single",
                        "l2": f"each weight and its moments are distinct buffers ({peak_gb:.0f} GB in total), so every launch "
@@ -722,6 +730,8 @@ def main():
                     help="storage of the AdamW moments (int8 / fp8_block: codes + one fp32 absmax scale per row and 64 columns)")
     ap.add_argument("--group", default="layer", choices=["layer", "x", "none"],
                     help="weights per kernel launch: the projections of a decoder layer, the linears that share an input, or one")
+    ap.add_argument("--layers-per-launch", type=int, default=0,
+                    help="with --group layer: decoder layers per kernel launch (1 or 2; default 2)")
     ap.add_argument("--streams", type=int, default=4, help="streams the independent updates of a step are spread over")
     ap.add_argument("--gather-x", action="store_true",
                     help="N > 1: all-gather the feature-sharded X by NCCL inside the timed step")

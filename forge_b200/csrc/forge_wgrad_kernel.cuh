@@ -7,7 +7,7 @@
 // (src/fused_grad_optimizer/kernel.py:212-317 AdamW, :122-205 SGD, :324-478 int8 moments,
 // kernel_fp8_state.py:204-295 fp8 moments).  The reference launches one kernel per linear; one launch
 // here updates a GROUP of up to MAX_GROUP weights of the same kernel configuration (say the q / k / v
-// projections, or all seven projections of a decoder layer): the work units of the problems are
+// projections, or all seven projections of one or two decoder layers): the work units of the problems are
 // numbered one after the other, the roles look up the problem a unit belongs to, and the pipelines
 // (operand ring, state ring, accumulators) run on across problem boundaries, so the start-up and the
 // ragged end of a launch are paid once per group instead of once per weight.
@@ -204,7 +204,7 @@ __device__ __forceinline__ void st16_bytes(uint8_t* buf, int r, int g, const uin
 }
 
 // kernel parameters ------------------------------------------------------------------------------
-constexpr int MAX_GROUP = 8;   // weights per launch
+constexpr int MAX_GROUP = 16;   // weights per launch (two decoder layers of seven projections)
 
 // One weight of a launch.  The tensor maps live in the kernel's parameter space; a role passes the
 // address of the map of the problem it is working on to the copy engine.

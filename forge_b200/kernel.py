@@ -126,7 +126,7 @@ class DeviceHyper:
 
 class UpdateGroup:
     """Fused updates of several weights issued together (``forge_wgrad_update_group``): consecutive
-    entries of one kernel configuration share a launch, eight at most, so the fixed start-up and the
+    entries of one kernel configuration share a launch, sixteen at most, so the fixed start-up and the
     ragged end of a launch are paid once per group.  No reference counterpart: the reference launches
     one kernel per linear (``autograd.py:94-144``).
 

@@ -275,13 +275,15 @@ class FusedOptimizerManager:
                 self._device_hyper[key] = DeviceHyper(m.weight.device)
         return self
 
-    def group_updates(self, groups="layer", max_group: int = 8):
+    def group_updates(self, groups="layer", max_group: int = 16, layers_per_group: int = 1):
         """Issue the fused updates of several linears as ONE launch each (``forge_wgrad_update_group``):
         the start-up and ragged end of a launch are then paid once per group instead of once per
         weight, which is most of what the small projections (k, v; every row shard in tensor-parallel
         mode) cost.  ``groups`` is a list of lists of ``FusedLinear`` modules, or ``"layer"``: modules
         whose names share the prefix up to their last numeric component (``model.layers.17.`` ...)
-        form a group, largest weights first, at most ``max_group`` (<= 8) per launch.  Members must
+        form a group, largest weights first, at most ``max_group`` (<= 16) per launch;
+        ``layers_per_group=2`` puts two consecutive numbered blocks into one launch (smaller shards in
+        tensor-parallel mode: fewer, larger launches).  Members must
         share optimizer type, state mode, weight dtype and device.  A group launches when its last
         member's backward has run; ``pre_step`` (and ``flush_updates``) issue anything left over.
         Results are bit-identical to ungrouped launches.  No reference counterpart."""
@@ -297,7 +299,8 @@ class FusedOptimizerManager:
                 idx = [i for i, p in enumerate(parts) if p.isdigit()]
                 if not idx:
                     continue
-                key = (".".join(parts[: idx[-1] + 1]), self._group_key(m), m.state_mode, m.weight.dtype)
+                block = parts[: idx[-1]] + [str(int(parts[idx[-1]]) // max(1, layers_per_group))]
+                key = (".".join(block), self._group_key(m), m.state_mode, m.weight.dtype)
                 by_prefix.setdefault(key, []).append(m)
             groups = []
             for members in by_prefix.values():
@@ -307,8 +310,8 @@ class FusedOptimizerManager:
             members = list(members)
             if len(members) < 2:
                 continue
-            if len(members) > 8:
-                raise ValueError("a group holds at most 8 linears")
+            if len(members) > 16:
+                raise ValueError("a group holds at most 16 linears")
             first = members[0]
             for m in members:
                 if not isinstance(m, FusedLinear) or id(m) not in self._fused_module_names:

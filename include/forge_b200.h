@@ -126,7 +126,7 @@ int forge_hyper_pack(const ForgeHyper* h, void* out);
 int forge_wgrad_update(const ForgeWgradArgs* args, void* cuda_stream);
 
 /* Weights one kernel launch of forge_wgrad_update_group covers. */
-#define FORGE_MAX_GROUP 8
+#define FORGE_MAX_GROUP 16
 
 /* The fused update of `count` weights in as few launches as possible: consecutive entries that agree
  * in w_dtype, optimizer and state mode share one launch, FORGE_MAX_GROUP at most, so that the fixed

@@ -122,11 +122,11 @@ def test_group_of_mixed_configurations_splits_into_launches():
 
 
 def test_group_larger_than_one_launch_and_fp32_operands():
-    """Eleven members (more than one launch holds) with fp32 dY / X: every member gets a split area
+    """Nineteen members (more than one launch holds) with fp32 dY / X: every member gets a split area
     of its own for the time the group is pending."""
     gen = torch.Generator(device=DEV).manual_seed(23)
     probs = []
-    for i in range(11):
+    for i in range(19):
         V, H = 128 + 8 * i, 256
         probs.append((torch.randn(48, V, device=DEV, generator=gen), torch.randn(48, H, device=DEV, generator=gen),
                       torch.randn(V, H, device=DEV, generator=gen), torch.zeros(V, H, device=DEV), torch.zeros(V, H, device=DEV)))
@@ -138,7 +138,7 @@ def test_group_larger_than_one_launch_and_fp32_operands():
         for i, (dy, x, *_r) in enumerate(probs):
             K.fused_grad_adamw(dy, x, *grouped[i], **ADAMW)
     torch.cuda.synchronize()
-    for i in range(11):
+    for i in range(19):
         _assert_same(single[i], grouped[i], f"member {i}")
 
 
