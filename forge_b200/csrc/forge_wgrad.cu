@@ -164,7 +164,7 @@ static int launch_wgrad(const Prepared* items, int n, int sm_count, cudaStream_t
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

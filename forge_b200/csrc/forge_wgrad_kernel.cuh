@@ -64,9 +64,12 @@ constexpr int UMMA_K = 16;
 #endif
 constexpr int OP_BK = FORGE_OP_BK;           // token rows per operand pipeline stage
 constexpr int OP_STAGES = FORGE_OP_STAGES;   // operand pipeline depth
-constexpr int NUM_THREADS = 384;
 constexpr int EPI_WARP0 = 4;
-constexpr int NUM_EPI_WARPS = 8;
+// 1: sixteen epilogue warps for the block-quantised modes (see WgradCfg::kWide).  Off: measured slower
+// (14336 x 4096 int8: 183 us against 160 us), although correct.
+#ifndef FORGE_WIDE_EPILOGUE
+#define FORGE_WIDE_EPILOGUE 0
+#endif
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BUDGET = 227 * 1024;
 
@@ -250,6 +253,16 @@ struct WgradCfg {
   static constexpr int kWES = (W_DT == DT_BF16) ? 2 : 4;
   static constexpr int kNMom = num_moments(OPT);
   static constexpr int kSES = state_elem_size(ST);
+  // Epilogue warps: eight (two groups of four, one accumulator row per thread).  With
+  // FORGE_WIDE_EPILOGUE the block-quantised modes take sixteen (two groups of eight): TWO lanes of a
+  // warp then share a row (tcgen05.ld shape 16x32bx2), 32 columns of the 64-column quantisation block
+  // each, the block absmax is agreed by one shuffle, a thread carries half the values and every
+  // scheduler has four epilogue warps.  It gives the same bits and is kept as a measured experiment:
+  // at the 96 registers that 640 threads leave it spills, executes 24 % more instructions, and the
+  // issue rate stays at 0.42 per scheduler and cycle as with eight warps, so it is slower.
+  static constexpr bool kWide = FORGE_WIDE_EPILOGUE && (ST == ST_INT8 || ST == ST_FP8_BLOCK) && (W_DT == DT_BF16);
+  static constexpr int kEpiWarps = kWide ? 16 : 8;
+  static constexpr int kThreads = (EPI_WARP0 + kEpiWarps) * 32;
   // Token rows per operand stage.  With at most one moment (SGD, momentum, Lion) the state stream
   // is short and the kernel is bound by the panel loads; what limits those is the number of copy
   // operations one thread can issue (four per stage), so these optimizers take 64 rows per stage:
@@ -314,12 +327,11 @@ struct alignas(16) CtrlBlock {
 static_assert(sizeof(CtrlBlock) <= 1024, "control block must fit in its reserved kilobyte");
 
 // roles other than the scheduler that read the unit queue, per CTA: MMA issuer (leader) or operand
-// producer (second CTA of a pair), state producer, store issuer, eight epilogue warps
-constexpr int TQ_READERS_PER_CTA = 3 + NUM_EPI_WARPS;
+// producer (second CTA of a pair), state producer, store issuer, the epilogue warps
 
 // ------------------------------------------------------------------------------------------------
 template <int W_DT, int ST, int OPT, int CG>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__((WgradCfg<W_DT, ST, OPT, CG>::kThreads), 1)
 forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
   using Cfg = WgradCfg<W_DT, ST, OPT, CG>;
   constexpr int BK = Cfg::kBK;
@@ -334,6 +346,10 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
   constexpr int SRB = Cfg::kSRB;
   constexpr int WBC = BoxGeom<WRB>::kBoxRowBytes / WES;                 // columns per W box
   constexpr int SBC = (NMOM > 0) ? BoxGeom<SRB>::kBoxRowBytes / (SES > 0 ? SES : 1) : 1;
+  constexpr bool WIDE = Cfg::kWide;
+  constexpr int NUM_EPI_WARPS = Cfg::kEpiWarps;
+  constexpr int GROUP_WARPS = NUM_EPI_WARPS / 2;          // warps that update one chunk together
+  constexpr int TQ_READERS_PER_CTA = 3 + NUM_EPI_WARPS;
   constexpr int A_BYTES = TILE_M * BK * 2;
   constexpr int SLAB_BYTES = 64 * BK * 2;  // one 64-element M/N slab of a K panel
 
@@ -358,7 +374,7 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
     for (int i = 0; i < NSS; ++i) {
       mbar_init(&ctrl->st_full[i], 1);
       mbar_init(&ctrl->st_empty[i], 1);
-      mbar_init(&ctrl->st_done[i], 4);   // one arrival per warp of the group that updated the chunk
+      mbar_init(&ctrl->st_done[i], GROUP_WARPS);   // one arrival per warp of the group that updated the chunk
     }
     for (int i = 0; i < 2; ++i) { mbar_init(&ctrl->acc_full[i], 1); mbar_init(&ctrl->acc_empty[i], NUM_EPI_WARPS * CG); }
     for (int i = 0; i < TQ_SLOTS; ++i) { mbar_init(&ctrl->tq_full[i], 1); mbar_init(&ctrl->tq_empty[i], TQ_READERS_PER_CTA * CG); }
@@ -658,8 +674,12 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
   } else if (warp >= EPI_WARP0) {
     // ------------------------------------------------------------------ epilogue
     const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
-    const int wg = (warp - EPI_WARP0) >> 2;       // 0 or 1
-    const int r = quarter * 32 + lane;            // row inside the tile
+    const int wg = (warp - EPI_WARP0) / GROUP_WARPS;       // 0 or 1: the chunks this warp's group takes
+    // row inside the tile, and -- wide form -- which 32 columns of the chunk this lane has
+    const int hh = WIDE ? (((warp - EPI_WARP0) % GROUP_WARPS) >> 2) : 0;      // 16-row half of the quarter
+    const int ch = WIDE ? (lane >> 4) : 0;
+    const int r = WIDE ? (quarter * 32 + hh * 16 + (lane & 15)) : (quarter * 32 + lane);
+    const uint32_t tmem_lane = static_cast<uint32_t>(WIDE ? (quarter * 32 + hh * 16) : (quarter * 32)) << 16;
     // per-problem values, (re)loaded when the unit at hand belongs to another problem than the last
     const WgradProblem* cur = nullptr;
     Hyper hy = gp.prob[0].hyper;
@@ -771,9 +791,10 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
         constexpr bool kTmemScratch = (ST == ST_INT8 || ST == ST_FP8_BLOCK);
         constexpr int ACC_REGS = kTmemScratch ? 16 : CN;
         uint32_t acc[ACC_REGS];
-        const uint32_t acc_taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(buf * TILE_N + c * CN);
-        if constexpr (kTmemScratch) {
+        const uint32_t acc_taddr = tmem_base + tmem_lane + static_cast<uint32_t>(buf * TILE_N + c * CN);
+        if constexpr (WIDE) {
+          tmem_ld_16x16_split32(acc_taddr, &acc[0]);
+        } else if constexpr (kTmemScratch) {
           tmem_ld_32x16(acc_taddr, &acc[0]);
         } else {
           tmem_ld_32x32(acc_taddr, &acc[0]);
@@ -872,27 +893,38 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
             if (g + 1 < NG) { rw = nw; rm = nm; rv = nv; }
           }
         } else if constexpr (ST == ST_INT8 || ST == ST_FP8_BLOCK) {
-          // The 64-column quantisation block is this thread's whole chunk row.  Pass 1 dequantises,
-          // updates W and tracks the block absmax; the new second moments stay in registers (they
-          // replace the accumulator values they were computed from), the new first moments are
-          // parked in the accumulator's own tensor-memory columns, which this thread has already
-          // read (holding both in registers spilled).  Pass 2 requantises them with the new scale.
-          // No shuffles, no recomputation.
+          // The 64-column quantisation block is this thread's whole chunk row -- or, in the wide form,
+          // the row of two lanes of this warp (lane and lane ^ 16), 32 columns each.  Pass 1 dequantises,
+          // updates W and tracks the block absmax; the new second moments stay in registers, the new
+          // first moments are parked in the accumulator's own tensor-memory columns, which this thread
+          // has already read (holding both in registers spilled).  Pass 2 requantises them with the
+          // new scale.  No recomputation; one shuffle per block in the wide form, none otherwise.
+          constexpr int MYG = WIDE ? 2 : NG;            // 16-column groups per thread
+          const int g0 = WIDE ? 2 * ch : 0;             // this thread's first group inside the chunk row
           const float sm_old = (i == 0) ? sc_m[0] : sc_m[1];
           const float sv_old = (i == 0) ? sc_v[0] : sc_v[1];
           const float2 sm_old2 = make_float2(sm_old, sm_old), sv_old2 = make_float2(sv_old, sv_old);
           const uint32_t scratch = acc_taddr;
-          float vv[CN];
+          // 16 tensor-memory columns of group g (the wide form's split load adds the other lane's 32 itself)
+          auto tm_ld = [&](int g, uint32_t* dst) {
+            if constexpr (WIDE) tmem_ld_16x16_split32(scratch + 16 * g, dst);
+            else tmem_ld_32x16(scratch + 16 * g, dst);
+          };
+          auto tm_st = [&](int g, const uint32_t* src) {
+            if constexpr (WIDE) tmem_st_16x16_split32(scratch + 16 * g, src);
+            else tmem_st_32x16(scratch + 16 * g, src);
+          };
+          float vv[16 * MYG];
           float am = 0.0f, av = 0.0f;
 #pragma unroll
-          for (int g = 0; g < NG; ++g) {
+          for (int g = 0; g < MYG; ++g) {
             float w[16];
             uint32_t mq[4], vq[4], mnew[16], acc_next[16];
             // the accumulator columns of the next group are on their way while this one is worked on
-            if (g + 1 < NG) tmem_ld_32x16(acc_taddr + 16 * (g + 1), acc_next);
-            unpack16<WES>(load_raw<WES, WRB>(wb, r, g), w);
-            ld16_bytes(mb, r, g, mq);
-            ld16_bytes(vb, r, g, vq);
+            if (g + 1 < MYG) tm_ld(g + 1, acc_next);
+            unpack16<WES>(load_raw<WES, WRB>(wb, r, g0 + g), w);
+            ld16_bytes(mb, r, g0 + g, mq);
+            ld16_bytes(vb, r, g0 + g, vq);
             if constexpr (ST == ST_INT8) {
               // first moments are signed: flip the sign bits so that a byte reads as code + 128; second
               // moments are never negative and are taken as they are
@@ -925,27 +957,32 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
               am = fmax3(am, fabsf(m2.x), fabsf(m2.y));
               av = fmax3(av, v2.x, v2.y);          // second moments are sums of non-negative terms
             }
-            tmem_st_32x16(scratch + 16 * g, mnew);
-            store_raw<WES, WRB>(wb, r, g, pack16<WES>(w));
-            if (g + 1 < NG) {
+            tm_st(g, mnew);
+            store_raw<WES, WRB>(wb, r, g0 + g, pack16<WES>(w));
+            if (g + 1 < MYG) {
               tmem_ld_wait();
 #pragma unroll
               for (int k = 0; k < 16; ++k) acc[k] = no_tokens ? 0u : acc_next[k];
             }
           }
           tmem_st_wait();
+          if constexpr (WIDE) {
+            // the other half of the block lives in lane ^ 16
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 16));
+            av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 16));
+          }
           const float sm_new = (ST == ST_INT8) ? int8_scale(am) : fp8blk_scale(am);
           const float sv_new = (ST == ST_INT8) ? int8_scale(av) : fp8blk_scale(av);
           const float rsm = f_rcp(sm_new), rsv = f_rcp(sv_new);
           const float2 nsm2 = make_float2(-sm_new, -sm_new), nsv2 = make_float2(-sv_new, -sv_new);
           const float2 rsm2 = make_float2(rsm, rsm), rsv2 = make_float2(rsv, rsv);
           uint32_t mcur[16];
-          tmem_ld_32x16(scratch, mcur);
+          tm_ld(0, mcur);
 #pragma unroll
-          for (int g = 0; g < NG; ++g) {
+          for (int g = 0; g < MYG; ++g) {
             uint32_t mo[4], vo[4], mnext[16];
             tmem_ld_wait();
-            if (g + 1 < NG) tmem_ld_32x16(scratch + 16 * (g + 1), mnext);
+            if (g + 1 < MYG) tm_ld(g + 1, mnext);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int k = 4 * j;
@@ -962,9 +999,9 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
                 vo[j] = e4m3x2_code_bits(qv01.x, qv01.y) | (e4m3x2_code_bits(qv23.x, qv23.y) << 16);
               }
             }
-            st16_bytes(mb, r, g, mo);
-            st16_bytes(vb, r, g, vo);
-            if (g + 1 < NG) {
+            st16_bytes(mb, r, g0 + g, mo);
+            st16_bytes(vb, r, g0 + g, vo);
+            if (g + 1 < MYG) {
 #pragma unroll
               for (int k = 0; k < 16; ++k) mcur[k] = mnext[k];
             }
@@ -980,7 +1017,7 @@ forge_wgrad_kernel(const __grid_constant__ WgradGroup gp) {
           }
           {
             const int cb = (col0 >> 6) + c;
-            if (grow < pV && cb * 64 < pH) {
+            if (ch == 0 && grow < pV && cb * 64 < pH) {
               pp->m_scale[static_cast<size_t>(grow) * pp->ld_scale + cb] = sm_new;
               pp->v_scale[static_cast<size_t>(grow) * pp->ld_scale + cb] = sv_new;
             }
