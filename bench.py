@@ -422,9 +422,11 @@ def run_forge(args):
     # ---------------------------------------------------------------- the sharded mode's whole linear backward
     # What a row-sharded layer really runs in its backward, per set of linears that share an input
     # (q/k/v, o, gate/up, down, lm_head): the partial dX = sum_members dY_r W_r (library GEMM or
-    # forge_dgrad), its reduce-scatter over the ranks by NCCL on a communication stream, and the fused
-    # update of the members as one launch.  `regather` adds the all-gather of X for a design that keeps
-    # only activation shards between forward and backward.  At N = 1 the collectives vanish.
+    # forge_dgrad) and its reduce-scatter over the ranks by NCCL on a communication stream; the fused
+    # updates are recorded as the sets go by and issued once per launch group (two decoder layers), as
+    # FusedOptimizerManager.group_updates does in training.  `regather` adds the all-gather of X for a
+    # design that keeps only activation shards between forward and backward.  At N = 1 the collectives
+    # vanish.
     from forge_b200.autograd import _grad_input
     from forge_b200.tensor_parallel import reduce_scatter_features
     x_groups = []
@@ -443,7 +445,17 @@ def run_forge(args):
         start.record(main)
         tp_comm.wait_event(start)
         dx_free.clear()
+        pending = K.UpdateGroup()
+        waits = []            # gathers the recorded updates still have to wait for
+        launch_of = {i: li for li, ix in enumerate(launches_idx) for i in ix}
+        last_launch = None
         for gi, (grp, members) in enumerate(x_groups):
+            if "update" in parts and last_launch is not None and launch_of[members[0]] != last_launch:
+                for ev in waits:
+                    main.wait_event(ev)
+                waits.clear()
+                pending.flush()
+            last_launch = launch_of[members[0]]
             H = params[members[0]][2]
             x = x_full[H]
             if regather and world > 1:
@@ -478,11 +490,15 @@ def run_forge(args):
                 dx_free[key] = done
             if "update" in parts:
                 if regather and world > 1:
-                    main.wait_event(ev_x)
-                with K.UpdateGroup():
+                    waits.append(ev_x)
+                with pending.record():
                     for i in members:
                         name, V, _H, _g, r0, r1, w, m, v = params[i]
                         update(dys[r1 - r0], x, w, m, v)
+        if "update" in parts:
+            for ev in waits:
+                main.wait_event(ev)
+            pending.flush()
         end = torch.cuda.Event()
         end.record(tp_comm)
         main.wait_event(end)
@@ -657,8 +673,8 @@ def run_forge(args):
             n_rs = len(x_groups)
             act_full = sum(BT * params[m[0]][2] * 2 for _, m in x_groups)
             line["tp_step"] = {
-                "what": "per set of linears sharing an input: partial dX GEMM, NCCL reduce-scatter of dX on a communication "
-                        "stream, fused update of the set as one launch; *_alone are the same parts timed by themselves",
+                "what": "per set of linears sharing an input: partial dX GEMM and NCCL reduce-scatter of dX on a communication "
+                        "stream; fused updates issued once per launch group; *_alone are the same parts timed by themselves",
                 "ms": tp_ms["step"], "dx_gemm_alone_ms": tp_ms["dx_gemm"], "update_alone_ms": tp_ms["update"],
                 "reduce_scatter_alone_ms": tp_ms.get("reduce_scatter"), "reduce_scatters_per_step": n_rs if world > 1 else 0,
                 "ms_regather_x": tp_ms.get("step_regather_x"), "all_gather_x_alone_ms": tp_ms.get("all_gather_x"),
