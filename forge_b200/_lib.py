@@ -89,6 +89,18 @@ class ForgeWgradArgs(ctypes.Structure):
     ]
 
 
+class ForgeDgradSegment(ctypes.Structure):
+    _fields_ = [("dY", ctypes.c_void_p), ("W", ctypes.c_void_p), ("V", ctypes.c_int64), ("ld_dy", ctypes.c_int64),
+                ("ld_w", ctypes.c_int64)]
+
+
+class ForgeDgradScatterArgs(ctypes.Structure):
+    _fields_ = [("segments", ctypes.POINTER(ForgeDgradSegment)), ("count", ctypes.c_int32), ("BT", ctypes.c_int64),
+                ("H", ctypes.c_int64), ("slots", ctypes.POINTER(ctypes.c_void_p)),
+                ("arrivals", ctypes.POINTER(ctypes.c_void_p)), ("counter", ctypes.c_void_p), ("epoch", ctypes.c_void_p),
+                ("rank", ctypes.c_int32), ("world", ctypes.c_int32), ("status", ctypes.c_void_p)]
+
+
 class ForgeOptimArgs(ctypes.Structure):
     _fields_ = [
         ("grad", ctypes.c_void_p),
@@ -116,6 +128,12 @@ _SIGNATURES = {
     "forge_optimizer_update": (ctypes.c_int, [ctypes.POINTER(ForgeOptimArgs), ctypes.c_void_p]),
     "forge_fp8_prestep": (ctypes.c_int, [ctypes.c_void_p] * 5),
     "forge_dgrad": (ctypes.c_int, [ctypes.c_void_p] * 3 + [ctypes.c_int64] * 6 + [ctypes.c_void_p] * 2),
+    "forge_dgrad_sum": (ctypes.c_int, [ctypes.POINTER(ForgeDgradSegment), ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64,
+                                       ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]),
+    "forge_dgrad_scatter": (ctypes.c_int, [ctypes.POINTER(ForgeDgradScatterArgs), ctypes.c_void_p]),
+    "forge_reduce_slots": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int64] * 3 + [ctypes.c_int32, ctypes.c_void_p,
+                                                                                        ctypes.c_void_p]),
+    "forge_set_arrival_wait_ns": (ctypes.c_int, [ctypes.c_uint64]),
     "forge_rmsnorm_forward": (ctypes.c_int, [ctypes.c_void_p] * 3 + [ctypes.c_int64] * 4 + [ctypes.c_double, ctypes.c_void_p]),
     "forge_rmsnorm_backward": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int32] * 2 + [ctypes.c_int64] * 5
                                + [ctypes.c_double, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),

@@ -9,6 +9,23 @@
 //   warps 4-7   epilogue: tcgen05.ld, fp32 -> bf16, swizzled staging tile, one TMA store per warp
 // Four 128 x 128 fp32 accumulators live in tensor memory, so the MMAs of the next tile start while
 // the previous tile is still being written out.
+//
+// Two extensions beyond the single product:
+//   * up to MAX_SEG (dY_i, W_i) pairs are accumulated into one dX = sum_i dY_i W_i (the linears that
+//     share an input -- q / k / v, gate / up -- have one input gradient): the producer walks the
+//     segments' K ranges one after the other, the accumulator never leaves tensor memory;
+//   * SCATTER: the row-sharded tensor-parallel mode's reduce-scatter of dX, fused into the GEMM.  The
+//     columns of dX are cut into `world` feature blocks; the epilogue stores each 128 x 128 tile straight
+//     into the receive buffer of the rank that owns its block -- slot [this rank] of that rank's
+//     (world, BT, H / world) buffer -- with plain peer stores over NVLink (coalesced 256-byte runs from the
+//     staging tile; no bulk-tensor copies and no multicast touch peer memory).  When the last CTA of the
+//     launch has stored its last tile, one thread raises this rank's arrival word on every owner
+//     (st.release.sys).  forge_reduce_slots on the owner waits (bounded) for all `world` arrival words and
+//     adds the slots in rank order in fp32.  This replaces GEMM -> NCCL reduce-scatter
+//     (src/fused_grad_optimizer/autograd.py:55 followed by a collective the reference does not have).
+#include <cuda_bf16.h>
+#include <string.h>
+
 #include <algorithm>
 #include <atomic>
 
@@ -30,7 +47,9 @@ constexpr int SMEM_BYTES = CTRL_BYTES + 1024 + STAGES * STAGE_BYTES + OUT_BYTES;
 constexpr int THREADS = 256;
 constexpr int ACC_BUFS = 4;
 constexpr int TMEM_COLS = 512;
-enum : int { ERR_OP_EMPTY = 201, ERR_OP_FULL = 202, ERR_ACC_EMPTY = 203, ERR_ACC_FULL = 204 };
+constexpr int MAX_SEG = 4;     // (dY_i, W_i) pairs accumulated into one dX
+constexpr int MAX_RANKS = 8;
+enum : int { ERR_OP_EMPTY = 201, ERR_OP_FULL = 202, ERR_ACC_EMPTY = 203, ERR_ACC_FULL = 204, ERR_ARRIVAL = 211 };
 
 struct Ctrl {
   uint64_t full[STAGES];
@@ -41,16 +60,30 @@ struct Ctrl {
   int abort_word;
 };
 
+struct alignas(64) Segment {
+  CUtensorMap tm_a;     // dY_i: (BT, V_i), boxes of BK columns x BM rows
+  CUtensorMap tm_b;     // W_i: (V_i, H), boxes of 64 columns x BK rows
+  int num_kb;           // ceil(V_i / BK)
+};
+
 struct Params {
-  int M, N, K;
-  int tiles_m, tiles_n, num_kb;
+  int M, N;
+  int tiles_m, tiles_n;
+  int nseg, total_kb;
   int* status;
+  // SCATTER
+  int rank, world, block_cols;                 // block_cols = N / world, a multiple of BN
+  uint8_t* slots[MAX_RANKS];                   // receive buffer of every rank, (world, M, block_cols) bf16
+  uint32_t* arrivals[MAX_RANKS];               // arrival words of every rank, `world` each; [rank] is written here
+  uint32_t* counter;                           // local: CTAs of this launch that have finished
+  const uint32_t* epoch;                       // local device word: the value raised
+  Segment seg[MAX_SEG];
 };
 }  // namespace dg
 
+template <bool SCATTER>
 __global__ void __launch_bounds__(dg::THREADS, 1)
-forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                   const __grid_constant__ CUtensorMap tm_out, const dg::Params p) {
+forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ dg::Params p) {
   using namespace dg;
   extern __shared__ uint8_t smem_raw[];
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw);
@@ -70,7 +103,11 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     tmem_alloc(&ctrl->tmem_base, TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == 0 && lane == 0) { prefetch_tmap(&tm_a); prefetch_tmap(&tm_b); prefetch_tmap(&tm_out); }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&p.seg[0].tm_a);
+    prefetch_tmap(&p.seg[0].tm_b);
+    if (!SCATTER) prefetch_tmap(&tm_out);
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -86,16 +123,22 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         // consecutive CTAs share a column panel of W: tile index runs over M fastest
         const int m0 = (tile % p.tiles_m) * BM;
         const int n0 = (tile / p.tiles_m) * BN;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&ctrl->empty[s], ph ^ 1, abort_word, ERR_OP_EMPTY)) goto done;
-          uint8_t* a = data + s * STAGE_BYTES;
-          uint8_t* b = a + A_BYTES;
-          mbar_expect_tx(&ctrl->full[s], STAGE_BYTES);
-          tma_load_2d(a, &tm_a, &ctrl->full[s], kb * BK, m0, pol_a);
-          tma_load_2d(b, &tm_b, &ctrl->full[s], n0, kb * BK, pol_b);
-          tma_load_2d(b + B_SLAB, &tm_b, &ctrl->full[s], n0 + 64, kb * BK, pol_b);
+        for (int sg = 0; sg < p.nseg; ++sg) {
+          const CUtensorMap* tm_a = &p.seg[sg].tm_a;
+          const CUtensorMap* tm_b = &p.seg[sg].tm_b;
+          const int nkb = p.seg[sg].num_kb;
+          for (int kb = 0; kb < nkb; ++kb, ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            if (!mbar_wait(&ctrl->empty[s], ph ^ 1, abort_word, ERR_OP_EMPTY)) goto done;
+            uint8_t* a = data + s * STAGE_BYTES;
+            uint8_t* b = a + A_BYTES;
+            mbar_expect_tx(&ctrl->full[s], STAGE_BYTES);
+            // rows / columns past the end of a segment are zero-filled and add nothing
+            tma_load_2d(a, tm_a, &ctrl->full[s], kb * BK, m0, pol_a);
+            tma_load_2d(b, tm_b, &ctrl->full[s], n0, kb * BK, pol_b);
+            tma_load_2d(b + B_SLAB, tm_b, &ctrl->full[s], n0 + 64, kb * BK, pol_b);
+          }
         }
       }
     }
@@ -109,7 +152,7 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         if (!mbar_wait(&ctrl->acc_empty[buf], aph ^ 1, abort_word, ERR_ACC_EMPTY)) goto done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+        for (int kb = 0; kb < p.total_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&ctrl->full[s], ph, abort_word, ERR_OP_FULL)) goto done;
@@ -145,14 +188,16 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       if (!ok) break;
       tc_fence_after();
       // the previous tile's store of this warp's rows must have been read out of the staging tile
-      if (lane == 0) tma_store_wait_read<0>();
+      if constexpr (!SCATTER) {
+        if (lane == 0) tma_store_wait_read<0>();
+      }
       __syncwarp();
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t acc[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + c * 32, acc);
         tmem_ld_wait();
-        if (p.num_kb == 0) {
+        if (p.total_kb == 0) {
 #pragma unroll
           for (int k = 0; k < 32; ++k) acc[k] = 0u;
         }
@@ -171,20 +216,44 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         }
       }
       tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&ctrl->acc_empty[buf]);
-        const int rr = m0 + quarter * 32;
-        if (rr < p.M) {
-          if (n0 < p.N) tma_store_2d(&tm_out, out_buf + quarter * 32 * 128, n0, rr, pol);
-          if (n0 + 64 < p.N) tma_store_2d(&tm_out, out_buf + BM * 128 + quarter * 32 * 128, n0 + 64, rr, pol);
+      if constexpr (!SCATTER) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&ctrl->acc_empty[buf]);
+          const int rr = m0 + quarter * 32;
+          if (rr < p.M) {
+            if (n0 < p.N) tma_store_2d(&tm_out, out_buf + quarter * 32 * 128, n0, rr, pol);
+            if (n0 + 64 < p.N) tma_store_2d(&tm_out, out_buf + BM * 128 + quarter * 32 * 128, n0 + 64, rr, pol);
+          }
+          tma_store_commit();
         }
-        tma_store_commit();
+        __syncwarp();
+      } else {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctrl->acc_empty[buf]);
+        // This warp's 32 rows of the staging tile go to the owner of the tile's feature block: slot
+        // [this rank] of its receive buffer, row m, column n - owner * block_cols.  Two rows per
+        // instruction, sixteen lanes x 16 bytes = one 256-byte run per row.
+        const int owner = n0 / p.block_cols;
+        uint8_t* dst = p.slots[owner] +
+                       (static_cast<size_t>(p.rank) * p.M * p.block_cols + (n0 - owner * p.block_cols)) * 2;
+        const int piece = lane & 15, bx = piece >> 3, pc = piece & 7;
+#pragma unroll 4
+        for (int rr = 0; rr < 32; rr += 2) {
+          const int row = quarter * 32 + rr + (lane >> 4);
+          const uint4 v = *reinterpret_cast<const uint4*>(out_buf + bx * (BM * 128) + row * 128 + ((pc ^ (row & 7)) << 4));
+          if (m0 + row < p.M)
+            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(m0 + row) * p.block_cols * 2 + piece * 16) = v;
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
-    if (lane == 0) tma_store_wait_all<0>();
+    if constexpr (!SCATTER) {
+      if (lane == 0) tma_store_wait_all<0>();
+    } else {
+      __threadfence_system();     // this thread's peer stores are visible system-wide before the CTA reports
+    }
   }
 
 done:
@@ -199,9 +268,73 @@ done:
     if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
     __syncthreads();
   }
+  if constexpr (SCATTER) {
+    // (the barrier above orders every epilogue warp's stores and fences before this)
+    if (threadIdx.x == 0 && *abort_word == 0) {
+      const uint32_t done = atomicAdd(p.counter, 1u);
+      if (done == gridDim.x - 1) {
+        // last CTA of the launch: everyone's tiles are out; tell every owner that this rank's slot is complete
+        __threadfence_system();
+        *p.counter = 0u;                         // ready for the next launch that uses this word
+        const uint32_t e = *p.epoch;
+        for (int o = 0; o < p.world; ++o)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.arrivals[o] + p.rank), "r"(e) : "memory");
+      }
+    }
+  }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// out[m, c] = sum over src = 0 .. world-1 of slot[src][m, c], added in that order in fp32, after every
+// source rank's arrival word has reached the epoch.  One thread per CTA waits (bounded, like every wait
+// of this library); a wait that runs out writes ERR_ARRIVAL to the status word and the CTA leaves its
+// part of `out` untouched.
+__global__ void __launch_bounds__(256)
+forge_reduce_slots_kernel(const uint8_t* __restrict__ slots, const uint32_t* arrivals, const uint32_t* epoch,
+                          __nv_bfloat16* __restrict__ out, int M, int S, long long ld_out, int world, int* status,
+                          unsigned long long limit_ns) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) {
+    const uint32_t e = *epoch;
+    int good = 1;
+    const uint64_t t0 = global_timer_ns();
+    for (int src = 0; src < world && good; ++src) {
+      for (uint32_t i = 0;; ++i) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(arrivals + src) : "memory");
+        if (v == e) break;
+        if ((i & 15u) == 15u && global_timer_ns() - t0 > limit_ns) { good = 0; break; }
+        __nanosleep(64);
+      }
+    }
+    if (!good && status != nullptr) atomicCAS(status, 0, dg::ERR_ARRIVAL);
+    ok = good;
+  }
+  __syncthreads();
+  if (!ok) return;
+  const long long pieces_per_row = S / 8;
+  const long long total = static_cast<long long>(M) * pieces_per_row;
+  const size_t slot_bytes = static_cast<size_t>(M) * S * 2;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long m = i / pieces_per_row, pc = i - m * pieces_per_row;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int src = 0; src < world; ++src) {
+      const uint4 q = *reinterpret_cast<const uint4*>(slots + src * slot_bytes + (m * S + pc * 8) * 2);
+      const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        acc[2 * k] += __uint_as_float(u[k] << 16);
+        acc[2 * k + 1] += __uint_as_float(u[k] & 0xFFFF0000u);
+      }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[k]) : "f"(acc[2 * k + 1]), "f"(acc[2 * k]));
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(out) + (m * ld_out + pc * 8) * 2) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -209,47 +342,136 @@ done:
 
 using namespace forge;
 
-extern "C" int forge_dgrad(const void* dY, const void* W, void* dX, int64_t BT, int64_t V, int64_t H,
-                           int64_t ld_dy, int64_t ld_w, int64_t ld_dx, int32_t* status, void* cuda_stream) {
+namespace {
+
+// validation, tensor maps of the segments and launch shared by the two entry points
+template <bool SCATTER>
+int launch_dgrad(const ForgeDgradSegment* segs, int nseg, void* dX, int64_t BT, int64_t H, int64_t ld_dx, dg::Params& p,
+                 int32_t* status, cudaStream_t stream) {
   using namespace forge::dg;
-  if (BT < 0 || V < 0 || H < 0) return fail(FORGE_ERR_INVALID_ARG, "negative dimension");
+  if (BT < 0 || H < 0 || nseg < 0) return fail(FORGE_ERR_INVALID_ARG, "negative dimension");
+  if (nseg > MAX_SEG) return fail(FORGE_ERR_INVALID_ARG, "at most %d (dY, W) pairs per launch (got %d)", MAX_SEG, nseg);
   if (BT == 0 || H == 0) return FORGE_OK;
-  if (dX == nullptr || (V > 0 && (dY == nullptr || W == nullptr))) return fail(FORGE_ERR_INVALID_ARG, "null pointer");
-  if (BT > (1 << 28) || V > (1ll << 30) || H > (1ll << 30)) return fail(FORGE_ERR_SHAPE, "dimension too large");
+  if (nseg > 0 && segs == nullptr) return fail(FORGE_ERR_INVALID_ARG, "segments pointer is NULL");
+  if (BT > (1 << 28) || H > (1ll << 30)) return fail(FORGE_ERR_SHAPE, "dimension too large");
   const DeviceInfo* di = current_device_info();
   if (di == nullptr) return FORGE_ERR_CUDA;
   if (di->cc_major != 10) return fail(FORGE_ERR_DEVICE, "device has compute capability %d.%d; sm_100 is required", di->cc_major, di->cc_minor);
-  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  CUtensorMap tm_a, tm_b, tm_out;
+  CUtensorMap tm_out;
+  memset(&tm_out, 0, sizeof(tm_out));
   int rc;
-  if ((rc = encode_tmap_2d(&tm_out, dX, 2, true, BT, H, ld_dx, 64, 32, 128)) != FORGE_OK) return rc;
-  if (V > 0) {
-    if ((rc = encode_tmap_2d(&tm_a, dY, 2, true, BT, V, ld_dy, BK, BM, 128)) != FORGE_OK) return rc;
-    if ((rc = encode_tmap_2d(&tm_b, W, 2, true, V, H, ld_w, 64, BK, 128)) != FORGE_OK) return rc;
-  } else {
-    tm_a = tm_out;
-    tm_b = tm_out;
+  if (!SCATTER) {
+    if (dX == nullptr) return fail(FORGE_ERR_INVALID_ARG, "dX is NULL");
+    if ((rc = encode_tmap_2d(&tm_out, dX, 2, true, BT, H, ld_dx, 64, 32, 128)) != FORGE_OK) return rc;
   }
-  Params p;
   p.M = static_cast<int>(BT);
   p.N = static_cast<int>(H);
-  p.K = static_cast<int>(V);
   p.tiles_m = static_cast<int>((BT + BM - 1) / BM);
   p.tiles_n = static_cast<int>((H + BN - 1) / BN);
-  p.num_kb = static_cast<int>((V + BK - 1) / BK);
+  p.nseg = 0;
+  p.total_kb = 0;
   p.status = status;
+  for (int i = 0; i < nseg; ++i) {
+    const ForgeDgradSegment& g = segs[i];
+    if (g.V < 0 || g.V > (1ll << 30)) return fail(FORGE_ERR_INVALID_ARG, "segment %d: bad V", i);
+    if (g.V == 0) continue;
+    if (g.dY == nullptr || g.W == nullptr) return fail(FORGE_ERR_INVALID_ARG, "segment %d: null pointer", i);
+    Segment& sg = p.seg[p.nseg++];
+    if ((rc = encode_tmap_2d(&sg.tm_a, g.dY, 2, true, BT, g.V, g.ld_dy, BK, BM, 128)) != FORGE_OK) return rc;
+    if ((rc = encode_tmap_2d(&sg.tm_b, g.W, 2, true, g.V, H, g.ld_w, 64, BK, 128)) != FORGE_OK) return rc;
+    sg.num_kb = static_cast<int>((g.V + BK - 1) / BK);
+    p.total_kb += sg.num_kb;
+  }
+  if (p.nseg == 0) {   // nothing to multiply: the maps are never used, pass valid memory anyway
+    p.seg[0].tm_a = tm_out;
+    p.seg[0].tm_b = tm_out;
+    p.seg[0].num_kb = 0;
+  }
+  auto kern = forge_dgrad_kernel<SCATTER>;
   static std::atomic<bool> attr_set[64];   // per device: the shared-memory opt-in has been made
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(forge_dgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_set[dev].store(true, std::memory_order_release);
   }
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   const int grid = static_cast<int>(std::min<int64_t>(tiles, di->sm_count));
-  forge_dgrad_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, tm_out, p);
+  kern<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_out, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "dgrad kernel launch: %s", cudaGetErrorString(e));
+  return FORGE_OK;
+}
+
+}  // namespace
+
+extern "C" int forge_dgrad(const void* dY, const void* W, void* dX, int64_t BT, int64_t V, int64_t H,
+                           int64_t ld_dy, int64_t ld_w, int64_t ld_dx, int32_t* status, void* cuda_stream) {
+  if (V < 0) return fail(FORGE_ERR_INVALID_ARG, "negative dimension");
+  ForgeDgradSegment seg = {dY, W, V, ld_dy, ld_w};
+  return forge_dgrad_sum(&seg, 1, dX, BT, H, ld_dx, status, cuda_stream);
+}
+
+extern "C" int forge_dgrad_sum(const ForgeDgradSegment* segments, int32_t count, void* dX, int64_t BT, int64_t H,
+                               int64_t ld_dx, int32_t* status, void* cuda_stream) {
+  dg::Params p;
+  memset(&p, 0, sizeof(p));
+  return launch_dgrad<false>(segments, count, dX, BT, H, ld_dx, p, status, static_cast<cudaStream_t>(cuda_stream));
+}
+
+extern "C" int forge_dgrad_scatter(const ForgeDgradScatterArgs* args, void* cuda_stream) {
+  using namespace forge::dg;
+  if (args == nullptr) return fail(FORGE_ERR_INVALID_ARG, "forge_dgrad_scatter: args is NULL");
+  const ForgeDgradScatterArgs& a = *args;
+  if (a.world < 1 || a.world > MAX_RANKS || a.rank < 0 || a.rank >= a.world)
+    return fail(FORGE_ERR_INVALID_ARG, "rank %d of %d (at most %d ranks)", a.rank, a.world, MAX_RANKS);
+  if (a.H <= 0 || a.H % a.world != 0 || (a.H / a.world) % BN != 0)
+    return fail(FORGE_ERR_SHAPE, "H (%lld) must split into %d feature blocks that are multiples of %d columns",
+                (long long)a.H, a.world, BN);
+  if (a.slots == nullptr || a.arrivals == nullptr || a.counter == nullptr || a.epoch == nullptr)
+    return fail(FORGE_ERR_INVALID_ARG, "forge_dgrad_scatter: slots / arrivals / counter / epoch is NULL");
+  dg::Params p;
+  memset(&p, 0, sizeof(p));
+  p.rank = a.rank;
+  p.world = a.world;
+  p.block_cols = static_cast<int>(a.H / a.world);
+  for (int r = 0; r < a.world; ++r) {
+    if (a.slots[r] == nullptr || a.arrivals[r] == nullptr || !aligned16(a.slots[r]))
+      return fail(FORGE_ERR_INVALID_ARG, "receive buffer or arrival words of rank %d are NULL or misaligned", r);
+    p.slots[r] = static_cast<uint8_t*>(a.slots[r]);
+    p.arrivals[r] = a.arrivals[r];
+  }
+  p.counter = a.counter;
+  p.epoch = a.epoch;
+  return launch_dgrad<true>(a.segments, a.count, nullptr, a.BT, a.H, 0, p, a.status, static_cast<cudaStream_t>(cuda_stream));
+}
+
+// time a reduce waits for its arrivals before it gives up (nanoseconds of the global timer)
+static std::atomic<uint64_t> g_arrival_wait_ns{FORGE_WAIT_NS};
+
+extern "C" int forge_set_arrival_wait_ns(uint64_t ns) {
+  if (ns == 0 || ns > 60000000000ull) return fail(FORGE_ERR_INVALID_ARG, "arrival wait must be 1 ns .. 60 s");
+  g_arrival_wait_ns.store(ns);
+  return FORGE_OK;
+}
+
+extern "C" int forge_reduce_slots(const void* slots, const uint32_t* arrivals, const uint32_t* epoch, void* out, int64_t BT,
+                                  int64_t block_cols, int64_t ld_out, int32_t world, int32_t* status, void* cuda_stream) {
+  if (slots == nullptr || arrivals == nullptr || epoch == nullptr || out == nullptr)
+    return fail(FORGE_ERR_INVALID_ARG, "forge_reduce_slots: null pointer");
+  if (world < 1 || world > dg::MAX_RANKS || BT < 0 || block_cols <= 0 || block_cols % 8 != 0 || ld_out % 8 != 0 ||
+      !aligned16(slots) || !aligned16(out))
+    return fail(FORGE_ERR_INVALID_ARG, "forge_reduce_slots: bad shape, world size or alignment");
+  if (BT == 0) return FORGE_OK;
+  const DeviceInfo* di = current_device_info();
+  if (di == nullptr) return FORGE_ERR_CUDA;
+  const int64_t pieces = BT * (block_cols / 8);
+  const int grid = static_cast<int>(std::min<int64_t>((pieces + 255) / 256, 2 * di->sm_count));
+  forge_reduce_slots_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint8_t*>(slots), arrivals, epoch, static_cast<__nv_bfloat16*>(out), static_cast<int>(BT),
+      static_cast<int>(block_cols), ld_out, world, status, g_arrival_wait_ns.load());
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "reduce kernel launch: %s", cudaGetErrorString(e));
   return FORGE_OK;
 }

@@ -453,6 +453,35 @@ def optimizer_only_lion(grad, weight, m, lr: float = 1e-4, beta1: float = 0.9, b
     _optim(grad, weight, OPT_LION, _moment_state(m), _hyper(lr, beta1, beta2, weight_decay=weight_decay))
 
 
+def dgrad_sum(members) -> torch.Tensor:
+    """``dX = sum_i dY_i @ W_i`` over one to four bf16 pairs in ONE launch (the input gradient of linears
+    that share their input: q / k / v, gate / up); the accumulator never leaves tensor memory."""
+    members = list(members)
+    if not 1 <= len(members) <= 4:
+        raise ValueError("one to four (dY, W) pairs")
+    dy0, w0 = members[0]
+    _require_cuda(dy0, w0)
+    BT, H = dy0.shape[0], w0.shape[1]
+    segs = (_lib.ForgeDgradSegment * len(members))()
+    for k, (dy, w) in enumerate(members):
+        _require_cuda(dy, w)
+        if dy.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            raise ValueError("dgrad_sum takes bfloat16 operands")
+        if dy.shape[0] != BT or w.shape[1] != H or dy.shape[1] != w.shape[0]:
+            raise ValueError(f"member {k}: shapes {tuple(dy.shape)} x {tuple(w.shape)} do not fit ({BT}, V) x (V, {H})")
+        _row_major_2d(dy, "dY")
+        _row_major_2d(w, "W")
+        segs[k].dY, segs[k].W, segs[k].V = dy.data_ptr(), w.data_ptr(), dy.shape[1]
+        segs[k].ld_dy, segs[k].ld_w = dy.stride(0), w.stride(0)
+    out = torch.empty(BT, H, dtype=torch.bfloat16, device=dy0.device)
+    lib = _lib.load()
+    with torch.cuda.device(w0.device):
+        rc = lib.forge_dgrad_sum(segs, len(members), out.data_ptr(), BT, H, out.stride(0),
+                                 _lib.status_word(w0.device).data_ptr(), _lib.current_stream_ptr(w0.device))
+    _lib.check(rc, "forge_dgrad_sum")
+    return out
+
+
 def dgrad(grad_output_2d: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``dX = dY @ W`` for bf16 operands through the library's own GEMM (``autograd.py:55``)."""
     _require_cuda(grad_output_2d, weight)

@@ -198,6 +198,56 @@ int forge_fp8_prestep(float* m_scale, float* v_scale, float* m_absmax_next, floa
 int forge_dgrad(const void* dY, const void* W, void* dX, int64_t BT, int64_t V, int64_t H,
                 int64_t ld_dy, int64_t ld_w, int64_t ld_dx, int32_t* status, void* cuda_stream);
 
+/* One (dY_i, W_i) pair of a summed input gradient. */
+typedef struct ForgeDgradSegment {
+  const void* dY;    /* (BT, V) bf16 */
+  const void* W;     /* (V, H) bf16 */
+  int64_t V;
+  int64_t ld_dy, ld_w;
+} ForgeDgradSegment;
+
+/* dX = sum_i dY_i W_i over up to 4 pairs in one launch, the accumulator staying in tensor memory: the
+ * input gradient of linears that share their input (q / k / v; gate / up).  Replaces the sum autograd
+ * forms from one `grad_output @ weight` per linear (src/fused_grad_optimizer/autograd.py:55). */
+int forge_dgrad_sum(const ForgeDgradSegment* segments, int32_t count, void* dX, int64_t BT, int64_t H, int64_t ld_dx,
+                    int32_t* status, void* cuda_stream);
+
+/* The row-sharded tensor-parallel mode's partial input gradient with its reduce-scatter fused into the
+ * GEMM (no counterpart in the reference, which has no distributed code).  The columns of dX are cut
+ * into `world` feature blocks of H / world columns (a multiple of 128); every 128 x 128 output tile is
+ * stored from the epilogue straight into the receive buffer of the rank that owns its block -- slot
+ * [rank] of that rank's (world, BT, H / world) bf16 buffer -- with plain peer stores; when the launch's
+ * last tile is out, this rank's arrival word on every owner is set to *epoch.
+ *   slots[o], arrivals[o]: rank o's receive buffer and its `world` arrival words, mapped into this
+ *     process (CUDA IPC or any peer mapping); entries [rank] are this rank's own memory.
+ *   counter: a local device word, zero before the first launch that uses it; the kernel leaves it zero.
+ *   epoch: a local device word holding the value to raise; change it between steps (e.g. add one inside
+ *     the captured graph) so that forge_reduce_slots can tell this step's arrival from the last one's.
+ * A receive buffer may be reused only after every rank has finished reading it (a collective of the
+ * next forward pass, or a barrier, between two uses is enough). */
+typedef struct ForgeDgradScatterArgs {
+  const ForgeDgradSegment* segments;
+  int32_t count;
+  int64_t BT, H;
+  void* const* slots;
+  uint32_t* const* arrivals;
+  uint32_t* counter;
+  const uint32_t* epoch;
+  int32_t rank, world;
+  int32_t* status;
+} ForgeDgradScatterArgs;
+int forge_dgrad_scatter(const ForgeDgradScatterArgs* args, void* cuda_stream);
+
+/* The owner's half of the fused reduce-scatter: waits (bounded; on expiry code 211 goes to *status)
+ * until all `world` arrival words equal *epoch, then out[m, c] = sum over src of slots[src][m, c], added
+ * in rank order in fp32 (bit-reproducible), as bf16. */
+int forge_reduce_slots(const void* slots, const uint32_t* arrivals, const uint32_t* epoch, void* out, int64_t BT,
+                       int64_t block_cols, int64_t ld_out, int32_t world, int32_t* status, void* cuda_stream);
+
+/* How long forge_reduce_slots waits for its arrival words before it gives up (default: two seconds;
+ * process-wide; tests shorten it). */
+int forge_set_arrival_wait_ns(uint64_t ns);
+
 /* RMSNorm recomputation for linears that fold their preceding norm (the normalised activation is not
  * kept between forward and backward): y = bf16(gamma * (x * rsqrt(mean(x^2) + eps))), fp32 inside;
  * x, gamma, y bf16; x and y (rows, H) row-major, H a multiple of 8 and at most 16384.  Replaces

@@ -64,3 +64,70 @@ def test_dgrad_strided_and_module_path():
     assert x.grad.shape == x.shape
     assert_one_ulp(expect.float().cpu(), x.grad, (gy.double().abs().reshape(-1, V) @ w0.double().abs()).reshape(4, 24, H).float().cpu(), "x.grad")
     assert not torch.equal(layer.weight.detach(), w0)
+
+
+@pytest.mark.parametrize("BT,H,Vs", [(512, 1024, (1024, 256, 256)), (200, 520, (136, 264)), (64, 256, (72, 8, 640, 128))])
+def test_dgrad_sum_of_several_pairs(BT, H, Vs):
+    """dX = sum_i dY_i W_i in one launch (q / k / v share their input gradient): exact-sum inputs, so the
+    bf16 result is unique whatever the accumulation order across and inside the segments."""
+    g = torch.Generator().manual_seed(24)
+    members, expect = [], torch.zeros(BT, H)
+    for V in Vs:
+        dy = (torch.randint(-8, 9, (BT, V), generator=g).float() / 8).bfloat16()
+        w = (torch.randint(-8, 9, (V, H), generator=g).float() / 8).bfloat16()
+        expect += dy.float() @ w.float()
+        members.append((dy.to(DEV), w.to(DEV)))
+    out = K.dgrad_sum(members)
+    assert torch.equal(out.cpu().view(torch.int16), expect.bfloat16().view(torch.int16))
+    with pytest.raises(ValueError):
+        K.dgrad_sum(members + members + members)
+
+
+def test_scatter_and_reduce_on_one_rank_equal_the_plain_gemm():
+    """The fused GEMM + reduce-scatter with a world of one: the epilogue's direct stores into the (only)
+    receive slot, the arrival word and the reduce kernel, against ``dgrad_sum`` bit for bit; and a reduce
+    whose arrival never comes gives up, reports code 211 and leaves its output untouched."""
+    import torch.distributed as dist
+    from forge_b200 import _lib
+    from forge_b200.peer import DgradReduceScatter
+    own_group = not dist.is_initialized()
+    if own_group:
+        import socket
+        sock = socket.socket()
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+        sock.close()
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
+    g = torch.Generator().manual_seed(25)
+    BT, H = 520, 1152
+    sets = [(BT, H), (BT, 256)]
+    rs = DgradReduceScatter(sets, device=torch.device(DEV, torch.cuda.current_device()))
+    for step in range(2):                       # the same buffers two steps in a row
+        rs.begin_step()
+        members = [((torch.randn(BT, V, generator=g) * 1e-2).bfloat16().to(DEV), (torch.randn(V, H, generator=g) * 0.02).bfloat16().to(DEV))
+                   for V in (392, 136)]
+        out = rs.run(0, members)
+        assert torch.equal(out.view(torch.int16), K.dgrad_sum(members).view(torch.int16))
+        small = [((torch.randn(BT, 64, generator=g)).bfloat16().to(DEV), (torch.randn(64, 256, generator=g)).bfloat16().to(DEV))]
+        assert torch.equal(rs.run(1, small).view(torch.int16), K.dgrad_sum(small).view(torch.int16))
+    torch.cuda.synchronize()
+    dev = torch.device(DEV, torch.cuda.current_device())
+    assert _lib.read_status(dev) == 0
+    # an arrival that never comes: the epoch moves on but nobody stores
+    lib = _lib.load()
+    rs.begin_step()
+    out = torch.full((BT, 256), 7.0, dtype=torch.bfloat16, device=DEV)
+    import ctypes
+    fn = lib.forge_reduce_slots
+    assert fn(rs.slots.data_ptr(), rs.arrivals.data_ptr(), rs.epoch.data_ptr(), None, BT, 256, 256, 1, None, None) == _lib.FORGE_ERR_INVALID_ARG
+    assert lib.forge_set_arrival_wait_ns(20_000_000) == 0          # 20 ms instead of the production two seconds
+    rc = fn(rs.slots.data_ptr() + rs._slot_off[1], rs.arrivals.data_ptr() + 4, rs.epoch.data_ptr(), out.data_ptr(), BT, 256, 256, 1,
+            _lib.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert (out == 7.0).all()
+    assert lib.forge_set_arrival_wait_ns(2_000_000_000) == 0
+    with pytest.raises(_lib.ForgeLibraryError, match="211"):
+        _lib.read_status(dev)
+    if own_group:
+        dist.destroy_process_group()

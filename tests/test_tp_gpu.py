@@ -94,3 +94,76 @@ def test_two_rank_nccl_matches_single_gpu(mode):
         if p.is_alive():
             p.terminate()
     assert sorted(out) == [(0, "ok"), (1, "ok")], out
+
+
+def _scatter_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=60))
+    try:
+        from forge_b200 import _lib
+        from forge_b200.peer import DgradReduceScatter
+        from forge_b200.tensor_parallel import reduce_scatter_features, row_range
+        BT, H = 384, 1024
+        Vs = (776, 264)                               # two linears sharing an input; unequal row shards
+        rs = DgradReduceScatter([(BT, H), (BT, H)], device=dev)
+        g = torch.Generator().manual_seed(11)         # the same full tensors on every rank
+        outs = []
+        for step in range(3):
+            rs.begin_step()
+            members, partial = [], torch.zeros(BT, H, dtype=torch.float64)
+            full_ref = torch.zeros(BT, H, dtype=torch.float64)
+            for V in Vs:
+                dy = (torch.randn(BT, V, generator=g) * 1e-2).bfloat16()
+                w = (torch.randn(V, H, generator=g) * 0.05).bfloat16()
+                full_ref += dy.double() @ w.double()
+                r0, r1 = row_range(V, rank, world)
+                members.append((dy[:, r0:r1].contiguous().to(dev), w[r0:r1].contiguous().to(dev)))
+            out = rs.run(step % 2, members)
+            # the NCCL path on the same partial products
+            part = sum((a.float() @ b.float() for a, b in members)).bfloat16()
+            ref_nccl = reduce_scatter_features(part)
+            s = H // world
+            ref = full_ref[:, rank * s:(rank + 1) * s]
+            err = (out.double().cpu() - ref).abs().max().item()
+            err_nccl = (ref_nccl.double().cpu() - ref).abs().max().item()
+            assert err <= 2.0 * err_nccl + 1e-4 * ref.abs().max().item(), (err, err_nccl)
+            outs.append(out.clone())
+            dist.barrier()                            # buffers alternate; a collective separates their reuse
+        torch.cuda.synchronize()
+        assert _lib.read_status(dev) == 0
+        dist.barrier()
+        q.put((rank, "ok"))
+        dist.destroy_process_group()
+    except Exception as e:  # pragma: no cover
+        import traceback
+        q.put((rank, f"{type(e).__name__}: {e} {traceback.format_exc()[-800:]}"))
+        os._exit(1)
+
+
+def test_two_rank_fused_dgrad_reduce_scatter():
+    """GEMM with the reduce-scatter fused into its epilogue (peer stores + arrival words) on two ranks:
+    as close to the exact sum as the library GEMM + NCCL reduce-scatter, three steps in a row."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_scatter_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = []
+    try:
+        for _ in procs:
+            out.append(q.get(timeout=150))
+            if out[-1][1] != "ok":
+                break
+    except Exception:
+        out.append(("parent", "timed out waiting for the ranks"))
+    for p in procs:
+        p.join(timeout=20)
+        if p.is_alive():
+            p.terminate()
+    assert sorted(out) == [(0, "ok"), (1, "ok")], out
