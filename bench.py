@@ -439,6 +439,47 @@ def run_forge(args):
     dx_bufs = {}       # (H, slot) -> partial dX buffer; two per width so the next GEMM does not wait for the last scatter
     dx_free = {}       # buffer -> event after the collective that last read it
 
+    # the same with the reduce-scatter fused into this library's dX GEMM (peer stores from the epilogue,
+    # forge_b200/peer.py): built on first use, where every feature block is a multiple of 128 columns
+    fused_rs = {}
+
+    def get_fused_rs():
+        if "rs" not in fused_rs:
+            from forge_b200.peer import DgradReduceScatter
+            fused_rs["rs"] = DgradReduceScatter([(BT, params[m[0]][2]) for _, m in x_groups], device=dev)
+            fused_rs["tick"] = torch.zeros(1, device=dev)
+        return fused_rs["rs"]
+
+    def step_tp_fused(step_no=None):
+        rs = get_fused_rs()
+        main = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(main)
+        tp_comm.wait_event(start)
+        rs.begin_step()
+        if world > 1:
+            # stands in for the collectives of the next forward pass: no rank overwrites a receive buffer
+            # that another rank is still reading from the step before
+            dist.all_reduce(fused_rs["tick"])
+        pending = K.UpdateGroup()
+        launch_of = {i: li for li, ix in enumerate(launches_idx) for i in ix}
+        last_launch = None
+        for gi, (grp, members) in enumerate(x_groups):
+            if last_launch is not None and launch_of[members[0]] != last_launch:
+                pending.flush()
+            last_launch = launch_of[members[0]]
+            H = params[members[0]][2]
+            # the owner's wait-and-sum runs beside the next set's GEMM, like the NCCL reduce-scatter above
+            rs.run(gi, [(dys[params[i][5] - params[i][4]], params[i][6]) for i in members], reduce_stream=tp_comm)
+            with pending.record():
+                for i in members:
+                    name, V, _H, _g, r0, r1, w, m, v = params[i]
+                    update(dys[r1 - r0], x_full[H], w, m, v)
+        pending.flush()
+        end = torch.cuda.Event()
+        end.record(tp_comm)
+        main.wait_event(end)
+
     def step_tp(step_no=None, parts=("dx", "rs", "update"), regather=False):
         main = torch.cuda.current_stream()
         start = torch.cuda.Event()
@@ -618,8 +659,11 @@ def run_forge(args):
         if world > 1:
             variants += [("step_regather_x", dict(regather=True)), ("reduce_scatter", dict(parts=("rs",))),
                          ("all_gather_x", dict(parts=(), regather=True))]
+        fused_ok = all(params[m[0]][2] % world == 0 and (params[m[0]][2] // world) % 128 == 0 and len(m) <= 4 for _, m in x_groups)
+        if fused_ok:
+            variants.append(("step_fused", None))
         for label, kw in variants:
-            fn = (lambda kw: (lambda step_no=None: step_tp(step_no, **kw)))(kw)
+            fn = step_tp_fused if kw is None else (lambda kw: (lambda step_no=None: step_tp(step_no, **kw)))(kw)
             set_step(step_no)
             fn()
             g_tp = capture(fn)
@@ -678,6 +722,9 @@ def run_forge(args):
                 "ms": tp_ms["step"], "dx_gemm_alone_ms": tp_ms["dx_gemm"], "update_alone_ms": tp_ms["update"],
                 "reduce_scatter_alone_ms": tp_ms.get("reduce_scatter"), "reduce_scatters_per_step": n_rs if world > 1 else 0,
                 "ms_regather_x": tp_ms.get("step_regather_x"), "all_gather_x_alone_ms": tp_ms.get("all_gather_x"),
+                "ms_fused_dx_reduce_scatter": tp_ms.get("step_fused"),
+                "fused": "forge_dgrad_scatter + forge_reduce_slots: this library's dX GEMM stores its tiles into the owner "
+                         "ranks' receive buffers over peer memory, no NCCL reduce-scatter",
                 "dx_gemm": "forge_dgrad" if __import__("forge_b200.autograd", fromlist=["x"]).use_forge_dgrad else "cuBLAS",
                 "saved_activation_bytes_per_rank": {"gathered_x": act_full, "x_shards": act_full // world},
                 "steps": tp_steps, "launch": "cuda_graph" if not args.eager else "eager"}

@@ -91,7 +91,10 @@ class DgradReduceScatter:
     def begin_step(self):
         self.epoch.add_(1)
 
-    def run(self, index: int, members, out: torch.Tensor | None = None) -> torch.Tensor:
+    def run(self, index: int, members, out: torch.Tensor | None = None, reduce_stream=None) -> torch.Tensor:
+        """``reduce_stream``: run the owner's wait-and-sum there (after the GEMM, by an event) so that the
+        current stream can go on while the peers' tiles are still arriving; the caller orders its use of
+        the result after that stream."""
         bt, h = self.sets[index]
         s = h // self.world
         if not 1 <= len(members) <= 4:
@@ -118,6 +121,11 @@ class DgradReduceScatter:
         with torch.cuda.device(self.device):
             stream = _lib.current_stream_ptr(self.device)
             _lib.check(lib.forge_dgrad_scatter(ctypes.byref(a), stream), "forge_dgrad_scatter")
+            if reduce_stream is not None:
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream(self.device))
+                reduce_stream.wait_event(ev)
+                stream = reduce_stream.cuda_stream
             _lib.check(lib.forge_reduce_slots(self.slots.data_ptr() + self._slot_off[index],
                                               self.arrivals.data_ptr() + 4 * index * self.world, self.epoch.data_ptr(),
                                               out.data_ptr(), bt, s, out.stride(0), self.world, status, stream),
