@@ -75,6 +75,9 @@ def main():
     ap.add_argument("--tp", type=int, default=0,
                     help="row-sharded tensor parallelism over this many ranks (launch with torch.distributed.run); "
                          "uses the decoder of examples/tp_model.py instead of the transformers model")
+    ap.add_argument("--fused-scatter", action="store_true",
+                    help="--tp: the input gradients of o and down through this library's dX GEMM with the reduce-scatter "
+                         "fused into its epilogue (peer stores) instead of a library GEMM + NCCL reduce-scatter")
     ap.add_argument("--no-group", action="store_true", help="one launch per linear instead of one per decoder layer")
     args = ap.parse_args()
     if args.tp:
@@ -196,6 +199,8 @@ def run_tp(args):
     if args.layers:
         cfg["layers"] = args.layers
     model = TPDecoder(cfg, state_mode=args.state, device=dev).train()
+    if args.fused_scatter and world > 1:
+        model.use_fused_scatter(args.seq)
     manager = FusedOptimizerManager(model)
     if not args.no_group:
         manager.group_updates("layer")
@@ -276,7 +281,8 @@ def run_tp(args):
             "median_ms_per_step": ms, "tokens_per_s": args.seq / (ms * 1e-3), "steps": args.steps,
             "peak_hbm_gb_per_rank": stats[1].item(), "first_loss": losses[0], "last_loss": losses[-1],
             "device_status": int(stats[2].item()), "cuda_graph": bool(graph is not None),
-            "grouped_launches": not args.no_group, "forge_dgrad": bool(args.forge_dgrad), "clocks": clocks,
+            "grouped_launches": not args.no_group, "forge_dgrad": bool(args.forge_dgrad),
+            "fused_scatter": bool(args.fused_scatter and world > 1), "clocks": clocks,
             "timing": "CUDA events per step, median over steps, max over ranks",
             "data": "synthetic uniform tokens (same on every rank), random init"}))
     sys.stdout.flush()

@@ -170,11 +170,12 @@ class Block(nn.Module):
         q, k = _rope(q, cos, sin), _rope(k, cos, sin)
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.nq != self.nkv)
         a = a.transpose(1, 2).reshape(B, T, self.nq * self.hd)
-        o = self.o(_GatherForShardedLinear.apply(a, self.group))
+        # (with a fused scatter attached, o and down gather their own input and return the scattered gradient)
+        o = self.o(a) if self.o.gather_input else self.o(_GatherForShardedLinear.apply(a, self.group))
         h = h + _GatherIntoReplicated.apply(o, self.group)
         x = _ToShardedLinears.apply(self.norm2(h), self.group)
         t = F.silu(self.gate(x)) * self.up(x)
-        d = self.down(_GatherForShardedLinear.apply(t, self.group))
+        d = self.down(t) if self.down.gather_input else self.down(_GatherForShardedLinear.apply(t, self.group))
         return h + _GatherIntoReplicated.apply(d, self.group)
 
 
@@ -205,6 +206,22 @@ class TPDecoder(nn.Module):
             if isinstance(m, RowShardedFusedLinear):
                 m.local.weight.data.normal_(0.0, 0.02, generator=gs)
 
+    def use_fused_scatter(self, tokens: int):
+        """Form the input gradients of o and down with the reduce-scatter fused into this library's dX
+        GEMM (``forge_b200.peer``) instead of a library GEMM + NCCL reduce-scatter.  ``tokens`` = batch x
+        sequence length of the steps to come (the receive buffers are sized for it).  Collective."""
+        from forge_b200.peer import DgradReduceScatter
+        sets, layers = [], []
+        for blk in self.layers:
+            for lin in (blk.o, blk.down):
+                sets.append((tokens, lin.in_features))
+                layers.append(lin)
+        self.fused_scatter = DgradReduceScatter(sets, group=self.group, device=self.embed.weight.device)
+        for i, lin in enumerate(layers):
+            lin.gather_input = True
+            lin.attach_fused_scatter(self.fused_scatter, i)
+        return self
+
     def head_sharded_norm_params(self):
         """Replicated parameters whose gradients are partial sums per rank (per-head q / k norms)."""
         return [p for blk in self.layers if blk.qk_norm for p in (blk.q_norm.weight, blk.k_norm.weight)]
@@ -216,6 +233,8 @@ class TPDecoder(nn.Module):
         ang = torch.arange(T, device=ids.device, dtype=torch.float32)[:, None] * inv[None, :]
         ang = torch.cat([ang, ang], dim=-1)
         cos, sin = ang.cos().to(self.embed.weight.dtype), ang.sin().to(self.embed.weight.dtype)
+        if getattr(self, "fused_scatter", None) is not None and self.training:
+            self.fused_scatter.begin_step()      # this step's arrivals are told from the last one's by the epoch
         h = self.embed(ids)
         for blk in self.layers:
             h = blk(h, cos, sin)

@@ -100,6 +100,39 @@ class _GatherX(torch.autograd.Function):
         return reduce_scatter_features(grad_full.contiguous(), ctx.group), None
 
 
+class _ShardedLinearFusedScatter(torch.autograd.Function):
+    """A row-sharded linear whose backward forms the reduce-scattered input gradient in one step:
+    forward = all-gather of the feature shards + ``F.linear`` on the local rows; backward = this
+    library's dX GEMM with the reduce-scatter fused into its epilogue (``forge_b200.peer``: tiles go
+    straight into the owner ranks' receive buffers over peer memory, the owner sums them in rank order)
+    followed by the fused update of the local rows.  Only the plain fused branch; the module falls back
+    to gather + ``FusedLinearFunction`` + NCCL reduce-scatter for everything else."""
+
+    @staticmethod
+    def forward(ctx, x_shard, weight, local, scatter, index, group):
+        x = all_gather_features(x_shard, group)
+        ctx.save_for_backward(x, weight)
+        ctx.local, ctx.scatter, ctx.index, ctx.shard_shape = local, scatter, index, x_shard.shape
+        return torch.nn.functional.linear(x, weight)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        from forge_b200.autograd import _apply_fused
+        x, weight = ctx.saved_tensors
+        local = ctx.local
+        dy2d = grad_output.reshape(-1, grad_output.shape[-1])
+        if not dy2d.is_contiguous():
+            dy2d = dy2d.contiguous()
+        x2d = x.reshape(-1, x.shape[-1])
+        # before the in-place update of `weight` on this stream
+        dx_shard = ctx.scatter.run(ctx.index, [(dy2d, weight.data)]).view(ctx.shard_shape)
+        if local._update_group is not None:
+            local._update_group.add(weight, lambda: _apply_fused(dy2d, x2d, weight, local._state, local._config))
+        else:
+            _apply_fused(dy2d, x2d, weight, local._state, local._config)
+        return dx_shard, None, None, None, None, None
+
+
 class RowShardedFusedLinear(nn.Module):
     """A ``FusedLinear`` holding only this rank's rows of the weight (and of its optimizer state).
 
@@ -141,7 +174,21 @@ class RowShardedFusedLinear(nn.Module):
     def weight(self):
         return self.local.weight
 
+    def attach_fused_scatter(self, scatter, index: int):
+        """Use ``scatter`` (a ``forge_b200.peer.DgradReduceScatter``), set ``index``, for this layer's input
+        gradient instead of a library GEMM followed by an NCCL reduce-scatter.  For layers that gather
+        their input (``gather_input=True``) with bf16 weights and no bias."""
+        self._scatter, self._scatter_index = scatter, index
+
     def forward(self, x):
+        sc = getattr(self, "_scatter", None)
+        loc = self.local
+        if (sc is not None and self.gather_input and self.world > 1 and loc.training and loc._config is not None
+                and not loc._is_accumulating and loc.use_fused_backward and loc.bias is None and x.is_cuda
+                and x.dtype == torch.bfloat16 and loc.weight.dtype == torch.bfloat16):
+            loc._ensure_state()
+            if loc._state._pending_grad is None:
+                return _ShardedLinearFusedScatter.apply(x, loc.weight, loc, sc, self._scatter_index, self.group)
         if self.gather_input and self.world > 1:
             x = _GatherX.apply(x, self.group)
         return self.local(x)

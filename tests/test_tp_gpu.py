@@ -167,3 +167,83 @@ def test_two_rank_fused_dgrad_reduce_scatter():
         if p.is_alive():
             p.terminate()
     assert sorted(out) == [(0, "ok"), (1, "ok")], out
+
+
+def _module_scatter_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=60))
+    try:
+        from forge_b200 import _lib
+        from forge_b200.peer import DgradReduceScatter
+        from forge_b200.tensor_parallel import RowShardedFusedLinear, feature_range
+        BT, H, V = 128, 512, 776
+        g = torch.Generator().manual_seed(7)
+        w0 = (torch.randn(V, H, generator=g) * 0.05).bfloat16()
+        plain = RowShardedFusedLinear.from_full_weight(w0.to(dev), optimizer_type="adamw", state_mode="int8").train()
+        fused = RowShardedFusedLinear.from_full_weight(w0.to(dev), optimizer_type="adamw", state_mode="int8").train()
+        rs = DgradReduceScatter([(BT, H)], device=dev)
+        fused.attach_fused_scatter(rs, 0)
+        c0, c1 = feature_range(H, rank, world)
+        for step in range(3):
+            x = torch.randn(BT, H, generator=g).bfloat16()
+            gy = (torch.randn(BT, V, generator=g) * 1e-2).bfloat16()
+            grads = []
+            for layer in (plain, fused):
+                layer.local.update_optimizer_config(lr=1e-2, weight_decay=0.01)
+                if layer is fused:
+                    rs.begin_step()
+                xin = x[:, c0:c1].to(dev).requires_grad_(True)
+                y = layer(xin)
+                if layer is fused:
+                    assert "ShardedLinearFusedScatter" in y.grad_fn.name()
+                y.backward(gy[:, layer.row_start:layer.row_end].to(dev))
+                grads.append(xin.grad)
+            ref = (gy.double() @ w0.double())[:, c0:c1] if step == 0 else None
+            scale = grads[0].float().abs().max().item()
+            assert (grads[0].float() - grads[1].float()).abs().max().item() <= 2e-2 * scale + 1e-6
+            dist.barrier()
+        # the update sees the same dY and the same gathered X on both paths: identical weights and states
+        assert torch.equal(plain.local.weight.data.view(torch.int16), fused.local.weight.data.view(torch.int16))
+        sa, sb = plain.local.get_optimizer_state_dict(), fused.local.get_optimizer_state_dict()
+        for k, v in sa.items():
+            if torch.is_tensor(v):
+                assert torch.equal(v.view(torch.uint8), sb[k].view(torch.uint8)), k
+        torch.cuda.synchronize()
+        assert _lib.read_status(dev) == 0
+        dist.barrier()
+        q.put((rank, "ok"))
+        dist.destroy_process_group()
+    except Exception as e:  # pragma: no cover
+        import traceback
+        q.put((rank, f"{type(e).__name__}: {e} {traceback.format_exc()[-800:]}"))
+        os._exit(1)
+
+
+def test_two_rank_sharded_linear_with_fused_scatter():
+    """``RowShardedFusedLinear`` with the fused GEMM + reduce-scatter attached against the same layer on
+    the library GEMM + NCCL path: the same weights and optimizer state bit for bit, input gradients
+    equal up to the rounding of the partial products."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_module_scatter_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = []
+    try:
+        for _ in procs:
+            out.append(q.get(timeout=150))
+            if out[-1][1] != "ok":
+                break
+    except Exception:
+        out.append(("parent", "timed out waiting for the ranks"))
+    for p in procs:
+        p.join(timeout=20)
+        if p.is_alive():
+            p.terminate()
+    assert sorted(out) == [(0, "ok"), (1, "ok")], out
