@@ -78,6 +78,9 @@ def main():
     ap.add_argument("--fused-scatter", action="store_true",
                     help="--tp: the input gradients of o and down through this library's dX GEMM with the reduce-scatter "
                          "fused into its epilogue (peer stores) instead of a library GEMM + NCCL reduce-scatter")
+    ap.add_argument("--fused-scatter-sets", choices=("all", "gathered"), default="all",
+                    help="--fused-scatter: 'gathered' keeps q/k/v and gate/up (replicated input) on library GEMMs + NCCL "
+                         "all-reduce; 'all' also forms their input gradient with one GEMM launch per set whose tiles go to every rank")
     ap.add_argument("--no-group", action="store_true", help="one launch per linear instead of one per decoder layer")
     args = ap.parse_args()
     if args.tp:
@@ -200,7 +203,7 @@ def run_tp(args):
         cfg["layers"] = args.layers
     model = TPDecoder(cfg, state_mode=args.state, device=dev).train()
     if args.fused_scatter and world > 1:
-        model.use_fused_scatter(args.seq)
+        model.use_fused_scatter(args.seq, replicated_sets=args.fused_scatter_sets == "all")
     manager = FusedOptimizerManager(model)
     if not args.no_group:
         manager.group_updates("layer")
@@ -244,6 +247,9 @@ def run_tp(args):
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
                     static_loss.copy_(one_step(static_ids).detach())
+                    left = sum(g.pending() for g in manager._update_groups)
+                    if left:     # an update outside the graph would never be replayed
+                        raise RuntimeError(f"{left} fused updates were still waiting for their group at the end of the backward pass")
                 graph.replay()
                 torch.cuda.synchronize()
                 losses.append(static_loss.item())
@@ -282,7 +288,7 @@ def run_tp(args):
             "peak_hbm_gb_per_rank": stats[1].item(), "first_loss": losses[0], "last_loss": losses[-1],
             "device_status": int(stats[2].item()), "cuda_graph": bool(graph is not None),
             "grouped_launches": not args.no_group, "forge_dgrad": bool(args.forge_dgrad),
-            "fused_scatter": bool(args.fused_scatter and world > 1), "clocks": clocks,
+            "fused_scatter": (args.fused_scatter_sets if args.fused_scatter and world > 1 else False), "clocks": clocks,
             "timing": "CUDA events per step, median over steps, max over ranks",
             "data": "synthetic uniform tokens (same on every rank), random init"}))
     sys.stdout.flush()

@@ -34,7 +34,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
-from forge_b200.tensor_parallel import (RowShardedFusedLinear, all_gather_features, feature_range,
+from forge_b200.tensor_parallel import (RowShardedFusedLinear, RowShardedLinearSet, all_gather_features, feature_range,
                                         reduce_scatter_features)
 
 
@@ -154,16 +154,24 @@ class Block(nn.Module):
         self.gate = RowShardedFusedLinear(hid, cfg["ffn"], **kw)
         self.up = RowShardedFusedLinear(hid, cfg["ffn"], **kw)
         self.down = RowShardedFusedLinear(cfg["ffn"], hid, **kw)
+        # the members that share a replicated input, for the fused input gradient (use_fused_scatter)
+        self.qkv_set = RowShardedLinearSet([self.q, self.k, self.v])
+        self.gu_set = RowShardedLinearSet([self.gate, self.up])
         self.qk_norm = cfg.get("qk_norm", False)
         if self.qk_norm:
             self.q_norm, self.k_norm = RMSNorm(hd, cfg["eps"]), RMSNorm(hd, cfg["eps"])
 
     def forward(self, h, cos, sin):
         B, T, _ = h.shape
-        x = _ToShardedLinears.apply(self.norm1(h), self.group)
-        q = self.q(x).view(B, T, self.nq, self.hd)
-        k = self.k(x).view(B, T, self.nkv, self.hd)
-        v = self.v(x).view(B, T, self.nkv, self.hd)
+        x = self.norm1(h)
+        if self.qkv_set.fused(x):
+            (q, k, v), _ = self.qkv_set(x)           # its backward returns the input gradient summed over the ranks
+        else:
+            x = _ToShardedLinears.apply(x, self.group)
+            q, k, v = self.q(x), self.k(x), self.v(x)
+        q = q.view(B, T, self.nq, self.hd)
+        k = k.view(B, T, self.nkv, self.hd)
+        v = v.view(B, T, self.nkv, self.hd)
         if self.qk_norm:
             q, k = self.q_norm(q), self.k_norm(k)
         q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
@@ -173,8 +181,13 @@ class Block(nn.Module):
         # (with a fused scatter attached, o and down gather their own input and return the scattered gradient)
         o = self.o(a) if self.o.gather_input else self.o(_GatherForShardedLinear.apply(a, self.group))
         h = h + _GatherIntoReplicated.apply(o, self.group)
-        x = _ToShardedLinears.apply(self.norm2(h), self.group)
-        t = F.silu(self.gate(x)) * self.up(x)
+        x = self.norm2(h)
+        if self.gu_set.fused(x):
+            (gate, up), _ = self.gu_set(x)
+        else:
+            x = _ToShardedLinears.apply(x, self.group)
+            gate, up = self.gate(x), self.up(x)
+        t = F.silu(gate) * up
         d = self.down(t) if self.down.gather_input else self.down(_GatherForShardedLinear.apply(t, self.group))
         return h + _GatherIntoReplicated.apply(d, self.group)
 
@@ -206,19 +219,26 @@ class TPDecoder(nn.Module):
             if isinstance(m, RowShardedFusedLinear):
                 m.local.weight.data.normal_(0.0, 0.02, generator=gs)
 
-    def use_fused_scatter(self, tokens: int):
+    def use_fused_scatter(self, tokens: int, replicated_sets: bool = True):
         """Form the input gradients of o and down with the reduce-scatter fused into this library's dX
-        GEMM (``forge_b200.peer``) instead of a library GEMM + NCCL reduce-scatter.  ``tokens`` = batch x
-        sequence length of the steps to come (the receive buffers are sized for it).  Collective."""
+        GEMM (``forge_b200.peer``) instead of a library GEMM + NCCL reduce-scatter, and those of q / k / v
+        and gate / up (replicated input) with one GEMM launch per set whose tiles go to every rank, instead
+        of one library GEMM per linear, autograd's additions and an NCCL all-reduce.  ``tokens`` = batch x
+        sequence length of the steps to come (the receive buffers are sized for it); ``replicated_sets=False``
+        leaves q / k / v and gate / up on the library path.  Collective."""
         from forge_b200.peer import DgradReduceScatter
         sets, layers = [], []
         for blk in self.layers:
-            for lin in (blk.o, blk.down):
+            for lin in (blk.o, blk.down):                 # input gathered from feature shards: reduce-scatter
                 sets.append((tokens, lin.in_features))
                 layers.append(lin)
+            for group in (blk.qkv_set, blk.gu_set) if replicated_sets else ():       # replicated input: all-reduce
+                sets.append((tokens, group.members[0].in_features, "allreduce"))
+                layers.append(group)
         self.fused_scatter = DgradReduceScatter(sets, group=self.group, device=self.embed.weight.device)
         for i, lin in enumerate(layers):
-            lin.gather_input = True
+            if isinstance(lin, RowShardedFusedLinear):
+                lin.gather_input = True
             lin.attach_fused_scatter(self.fused_scatter, i)
         return self
 

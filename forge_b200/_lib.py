@@ -98,7 +98,8 @@ class ForgeDgradScatterArgs(ctypes.Structure):
     _fields_ = [("segments", ctypes.POINTER(ForgeDgradSegment)), ("count", ctypes.c_int32), ("BT", ctypes.c_int64),
                 ("H", ctypes.c_int64), ("slots", ctypes.POINTER(ctypes.c_void_p)),
                 ("arrivals", ctypes.POINTER(ctypes.c_void_p)), ("counter", ctypes.c_void_p), ("epoch", ctypes.c_void_p),
-                ("rank", ctypes.c_int32), ("world", ctypes.c_int32), ("status", ctypes.c_void_p)]
+                ("rank", ctypes.c_int32), ("world", ctypes.c_int32), ("status", ctypes.c_void_p),
+                ("all_ranks", ctypes.c_int32)]
 
 
 class ForgeOptimArgs(ctypes.Structure):

@@ -133,10 +133,14 @@ class LayerUpdateGroup:
         self._members = {w.data_ptr() for w in weights}
         self._seen: set[int] = set()
         self._group = K.UpdateGroup()
-        # the same set for members whose backward runs in the C++ autograd node
+        # With the C++ autograd node built, ITS group object is the one that counts the members and
+        # launches: members whose backward runs in Python hand their recorded update to it, so a
+        # layer whose linears are split between the two paths still goes out as one launch, inside
+        # the backward pass (and therefore inside a captured graph of it).
         from forge_b200 import native
         nat = native.module()
         self.native = None
+        self._keep: list = []
         if nat is not None:
             self.native = nat.Group()
             self.native.set_members(sorted(self._members))
@@ -146,6 +150,18 @@ class LayerUpdateGroup:
 
     def add(self, weight, launch):
         wid = weight.data_ptr()
+        if self.native is not None:
+            with self._group.record():
+                launch()
+            blocks, keep, device = self._group.take()
+            if self.native.pending() == 0:
+                self._keep.clear()     # everything recorded before has been enqueued
+            self._keep.extend(keep)
+            for a in blocks:           # the native group flushes itself on a repeated or on the last member
+                self.native.add_recorded(bytes(a), torch.device(device).index)
+            if self.native.pending() == 0:
+                self._keep.clear()
+            return
         if wid in self._seen:          # the same linear twice in one pass: issue what is there first
             self.flush()
         with self._group.record():
@@ -154,11 +170,16 @@ class LayerUpdateGroup:
         if self._seen >= self._members:
             self.flush()
 
+    def pending(self) -> int:
+        """Updates recorded and not yet enqueued."""
+        return len(self._group) + (self.native.pending() if self.native is not None else 0)
+
     def flush(self):
         self._seen.clear()
         self._group.flush()
         if self.native is not None:
             self.native.flush()
+        self._keep.clear()
 
 
 def _begin_update(state, config):

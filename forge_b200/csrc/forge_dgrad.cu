@@ -73,6 +73,7 @@ struct Params {
   int* status;
   // SCATTER
   int rank, world, block_cols;                 // block_cols = N / world, a multiple of BN
+  int all_ranks;                               // 1: every tile goes to EVERY rank (slots are full width): a fused all-reduce
   uint8_t* slots[MAX_RANKS];                   // receive buffer of every rank, (world, M, block_cols) bf16
   uint32_t* arrivals[MAX_RANKS];               // arrival words of every rank, `world` each; [rank] is written here
   uint32_t* counter;                           // local: CTAs of this launch that have finished
@@ -235,16 +236,21 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
         // This warp's 32 rows of the staging tile go to the owner of the tile's feature block: slot
         // [this rank] of its receive buffer, row m, column n - owner * block_cols.  Two rows per
         // instruction, sixteen lanes x 16 bytes = one 256-byte run per row.
-        const int owner = n0 / p.block_cols;
-        uint8_t* dst = p.slots[owner] +
-                       (static_cast<size_t>(p.rank) * p.M * p.block_cols + (n0 - owner * p.block_cols)) * 2;
+        // (all_ranks: the tile goes to every rank's slot [this rank], which is then N columns wide)
         const int piece = lane & 15, bx = piece >> 3, pc = piece & 7;
+        const int first = p.all_ranks ? 0 : n0 / p.block_cols;
+        const int last = p.all_ranks ? p.world - 1 : first;
+        const int pitch = p.all_ranks ? p.N : p.block_cols;          // columns of a slot row
+        const int col = p.all_ranks ? n0 : n0 - first * p.block_cols;
+        for (int owner = first; owner <= last; ++owner) {
+          uint8_t* dst = p.slots[owner] + (static_cast<size_t>(p.rank) * p.M * pitch + col) * 2;
 #pragma unroll 4
-        for (int rr = 0; rr < 32; rr += 2) {
-          const int row = quarter * 32 + rr + (lane >> 4);
-          const uint4 v = *reinterpret_cast<const uint4*>(out_buf + bx * (BM * 128) + row * 128 + ((pc ^ (row & 7)) << 4));
-          if (m0 + row < p.M)
-            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(m0 + row) * p.block_cols * 2 + piece * 16) = v;
+          for (int rr = 0; rr < 32; rr += 2) {
+            const int row = quarter * 32 + rr + (lane >> 4);
+            const uint4 v = *reinterpret_cast<const uint4*>(out_buf + bx * (BM * 128) + row * 128 + ((pc ^ (row & 7)) << 4));
+            if (m0 + row < p.M && n0 + piece * 8 < p.N)
+              *reinterpret_cast<uint4*>(dst + static_cast<size_t>(m0 + row) * pitch * 2 + piece * 16) = v;
+          }
         }
         __syncwarp();
       }
@@ -426,16 +432,17 @@ extern "C" int forge_dgrad_scatter(const ForgeDgradScatterArgs* args, void* cuda
   const ForgeDgradScatterArgs& a = *args;
   if (a.world < 1 || a.world > MAX_RANKS || a.rank < 0 || a.rank >= a.world)
     return fail(FORGE_ERR_INVALID_ARG, "rank %d of %d (at most %d ranks)", a.rank, a.world, MAX_RANKS);
-  if (a.H <= 0 || a.H % a.world != 0 || (a.H / a.world) % BN != 0)
-    return fail(FORGE_ERR_SHAPE, "H (%lld) must split into %d feature blocks that are multiples of %d columns",
-                (long long)a.H, a.world, BN);
+  if (a.H <= 0 || a.H % 8 != 0 || (!a.all_ranks && (a.H % a.world != 0 || (a.H / a.world) % BN != 0)))
+    return fail(FORGE_ERR_SHAPE, "H (%lld) must split into %d feature blocks that are multiples of %d columns "
+                "(any multiple of 8 when every rank receives everything)", (long long)a.H, a.world, BN);
   if (a.slots == nullptr || a.arrivals == nullptr || a.counter == nullptr || a.epoch == nullptr)
     return fail(FORGE_ERR_INVALID_ARG, "forge_dgrad_scatter: slots / arrivals / counter / epoch is NULL");
   dg::Params p;
   memset(&p, 0, sizeof(p));
   p.rank = a.rank;
   p.world = a.world;
-  p.block_cols = static_cast<int>(a.H / a.world);
+  p.block_cols = static_cast<int>(a.all_ranks ? a.H : a.H / a.world);
+  p.all_ranks = a.all_ranks ? 1 : 0;
   for (int r = 0; r < a.world; ++r) {
     if (a.slots[r] == nullptr || a.arrivals[r] == nullptr || !aligned16(a.slots[r]))
       return fail(FORGE_ERR_INVALID_ARG, "receive buffer or arrival words of rank %d are NULL or misaligned", r);

@@ -170,6 +170,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              for (int64_t p : ptrs) g.members.insert(reinterpret_cast<const void*>(p));
            })
       .def("flush", &NativeGroup::flush)
+      .def("add_recorded",
+           [](NativeGroup& g, const std::string& bytes, int device) {
+             // an update recorded by a member whose backward ran in Python; the caller keeps its tensors alive
+             TORCH_CHECK(bytes.size() == sizeof(ForgeWgradArgs), "argument block of ", bytes.size(), " bytes, expected ",
+                         sizeof(ForgeWgradArgs));
+             ForgeWgradArgs a;
+             std::memcpy(&a, bytes.data(), sizeof(ForgeWgradArgs));
+             g.add(a, at::Tensor(), at::Tensor(), device);
+           })
       .def("pending", [](const NativeGroup& g) { return g.args.size(); });
   pybind11::class_<NativeLinear, std::shared_ptr<NativeLinear>>(m, "Linear")
       .def(pybind11::init<>())

@@ -180,6 +180,13 @@ class UpdateGroup:
         self._keep.clear()
         self._device = None
 
+    def take(self):
+        """Hand the recorded entries to the caller: ``(argument blocks, kept tensors, device)``; the
+        group is empty afterwards and the caller answers for the launch."""
+        out = (list(self._args), list(self._keep), self._device)
+        self.clear()
+        return out
+
     def flush(self):
         """Enqueue the recorded updates on the current stream of their device and forget them."""
         n = len(self._args)

@@ -50,8 +50,12 @@ def _share(t: torch.Tensor, group=None) -> list[torch.Tensor]:
 class DgradReduceScatter:
     """The input gradients of a step's linear sets, each ``dX[:, my block] = sum_r sum_i dY_r,i W_r,i``.
 
-    ``sets``: one ``(BT, H)`` per set of linears that share an input, in the order they are run.  Every
-    rank must construct this with the same list (collective).  ``begin_step()`` advances the epoch that
+    ``sets``: one ``(BT, H)`` or ``(BT, H, "allreduce")`` per set of linears that share an input.  The
+    plain form scatters: each rank ends up with its feature block ``(BT, H / world)`` of the summed
+    gradient (layers whose input was gathered from feature shards).  ``"allreduce"`` sends every tile to
+    every rank instead, and each rank sums the full ``(BT, H)`` itself -- one step instead of a
+    reduce-scatter followed by an all-gather -- for sets whose input is replicated (q / k / v, gate / up).
+    Every rank must construct this with the same list (collective).  ``begin_step()`` advances the epoch that
     tells this step's arrivals from the last one's (a one-element device add: it can sit inside a
     captured graph).  ``run(i, [(dY, W), ...])`` launches the GEMM + peer stores and the reduce on the
     current stream and returns this rank's ``(BT, H / world)`` block.
@@ -63,14 +67,21 @@ class DgradReduceScatter:
         if self.world > 8:
             raise ValueError("at most 8 ranks")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-        self.sets = [(int(bt), int(h)) for bt, h in sets]
-        for bt, h in self.sets:
-            if h % self.world or (h // self.world) % 128:
+        self.sets, self.all_ranks = [], []
+        for entry in sets:
+            bt, h = int(entry[0]), int(entry[1])
+            everywhere = len(entry) > 2 and entry[2] == "allreduce"
+            if everywhere:
+                if h % 8:
+                    raise ValueError(f"H ({h}) must be a multiple of 8")
+            elif h % self.world or (h // self.world) % 128:
                 raise ValueError(f"H ({h}) must split into {self.world} feature blocks that are multiples of 128 columns")
+            self.sets.append((bt, h))
+            self.all_ranks.append(everywhere)
         offs, total = [], 0
-        for bt, h in self.sets:
+        for (bt, h), everywhere in zip(self.sets, self.all_ranks):
             offs.append(total)
-            total += (bt * h * 2 + 255) // 256 * 256
+            total += (bt * h * 2 * (self.world if everywhere else 1) + 255) // 256 * 256
         self._slot_off = offs
         n = len(self.sets)
         self.slots = torch.zeros(max(total, 256), dtype=torch.uint8, device=self.device)
@@ -96,7 +107,8 @@ class DgradReduceScatter:
         current stream can go on while the peers' tiles are still arriving; the caller orders its use of
         the result after that stream."""
         bt, h = self.sets[index]
-        s = h // self.world
+        everywhere = self.all_ranks[index]
+        s = h if everywhere else h // self.world
         if not 1 <= len(members) <= 4:
             raise ValueError("one to four (dY, W) pairs per set")
         segs = (_lib.ForgeDgradSegment * len(members))()
@@ -113,6 +125,7 @@ class DgradReduceScatter:
         a.counter = self.counters.data_ptr() + 4 * index
         a.epoch = self.epoch.data_ptr()
         a.rank, a.world = self.rank, self.world
+        a.all_ranks = 1 if everywhere else 0
         status = _lib.status_word(self.device).data_ptr()
         a.status = status
         lib = _lib.load()

@@ -133,6 +133,81 @@ class _ShardedLinearFusedScatter(torch.autograd.Function):
         return dx_shard, None, None, None, None, None
 
 
+class _ShardedSetFusedAllReduce(torch.autograd.Function):
+    """Several row-sharded linears on one REPLICATED input (q / k / v; gate / up).  Forward: one
+    ``F.linear`` per member.  Backward: ONE launch of this library's dX GEMM accumulates
+    ``sum_i dY_i W_i`` over the members and stores every tile into every rank's receive buffer; each
+    rank then adds the ranks' partial sums itself (a fused all-reduce over peer memory: no per-linear
+    GEMMs, no autograd additions, no NCCL all-reduce); the members' fused updates follow."""
+
+    @staticmethod
+    def forward(ctx, x, scatter, index, locals_, *weights):
+        ctx.save_for_backward(x, *weights)
+        ctx.locals_, ctx.scatter, ctx.index = locals_, scatter, index
+        return tuple(torch.nn.functional.linear(x, w) for w in weights)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        from forge_b200.autograd import _apply_fused
+        x, *weights = ctx.saved_tensors
+        x2d = x.reshape(-1, x.shape[-1])
+        dys = []
+        for g, w in zip(grads, weights):
+            d = g.reshape(-1, w.shape[0])
+            dys.append(d if d.is_contiguous() else d.contiguous())
+        # before the in-place updates of the weights on this stream
+        dx = ctx.scatter.run(ctx.index, [(d, w.data) for d, w in zip(dys, weights)]).view(x.shape)
+        for d, w, loc in zip(dys, weights, ctx.locals_):
+            if loc._update_group is not None:
+                loc._update_group.add(w, lambda d=d, w=w, loc=loc: _apply_fused(d, x2d, w, loc._state, loc._config))
+            else:
+                _apply_fused(d, x2d, w, loc._state, loc._config)
+        return (dx, None, None, None) + (None,) * len(weights)
+
+
+class RowShardedLinearSet(nn.Module):
+    """Row-sharded linears that consume the same replicated activation.  Without a fused scatter attached
+    (or outside its conditions) it runs the members one by one; ``partial_input_grad`` tells the caller
+    whether the input gradient it gets back still has to be summed over the ranks.  The set does not
+    own its members (no parameters of its own), so a model that also holds them by name keeps one entry
+    per layer in its state dict."""
+
+    def __init__(self, members):
+        super().__init__()
+        if any(m.gather_input for m in members):
+            raise ValueError("the members of a set take a replicated input (gather_input=False)")
+        if len({m.in_features for m in members}) != 1:
+            raise ValueError("the members of a set share one input")
+        self.members = tuple(members)       # not registered here: the members stay owned by whoever built them
+        self._scatter, self._scatter_index = None, None
+
+    def attach_fused_scatter(self, scatter, index: int):
+        self._scatter, self._scatter_index = scatter, index
+
+    def fused(self, x) -> bool:
+        if self._scatter is None or not x.is_cuda or x.dtype != torch.bfloat16 or len(self.members) > 4:
+            return False
+        for m in self.members:
+            loc = m.local
+            if not (m.world > 1 and loc.training and loc._config is not None and not loc._is_accumulating
+                    and loc.use_fused_backward and loc.bias is None and loc.weight.dtype == torch.bfloat16):
+                return False
+            loc._ensure_state()
+            if loc._state._pending_grad is not None:
+                return False
+        return True
+
+    def forward(self, x):
+        """Returns ``(outputs, complete)``: the members' outputs and whether the input gradient that will
+        come back is already summed over the ranks (fused path) or still partial (plain path)."""
+        if self.fused(x):
+            locals_ = [m.local for m in self.members]
+            outs = _ShardedSetFusedAllReduce.apply(x, self._scatter, self._scatter_index, locals_,
+                                                   *[loc.weight for loc in locals_])
+            return outs, True
+        return tuple(m(x) for m in self.members), False
+
+
 class RowShardedFusedLinear(nn.Module):
     """A ``FusedLinear`` holding only this rank's rows of the weight (and of its optimizer state).
 

@@ -235,6 +235,9 @@ typedef struct ForgeDgradScatterArgs {
   const uint32_t* epoch;
   int32_t rank, world;
   int32_t* status;
+  int32_t all_ranks;   /* 1: a fused ALL-REDUCE instead -- every tile is stored into slot [rank] of EVERY rank's
+                          buffer, which is then (world, BT, H) wide, and forge_reduce_slots is called with
+                          block_cols = H; for a linear set whose input is replicated (q / k / v, gate / up) */
 } ForgeDgradScatterArgs;
 int forge_dgrad_scatter(const ForgeDgradScatterArgs* args, void* cuda_stream);
 

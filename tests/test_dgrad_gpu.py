@@ -100,7 +100,7 @@ def test_scatter_and_reduce_on_one_rank_equal_the_plain_gemm():
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
     g = torch.Generator().manual_seed(25)
     BT, H = 520, 1152
-    sets = [(BT, H), (BT, 256)]
+    sets = [(BT, H), (BT, 256), (BT, 1000, "allreduce")]
     rs = DgradReduceScatter(sets, device=torch.device(DEV, torch.cuda.current_device()))
     for step in range(2):                       # the same buffers two steps in a row
         rs.begin_step()
@@ -110,6 +110,12 @@ def test_scatter_and_reduce_on_one_rank_equal_the_plain_gemm():
         assert torch.equal(out.view(torch.int16), K.dgrad_sum(members).view(torch.int16))
         small = [((torch.randn(BT, 64, generator=g)).bfloat16().to(DEV), (torch.randn(64, 256, generator=g)).bfloat16().to(DEV))]
         assert torch.equal(rs.run(1, small).view(torch.int16), K.dgrad_sum(small).view(torch.int16))
+        # every-rank mode: slots are full width and H need not split into 128-column blocks
+        ragged = [((torch.randn(BT, V, generator=g) * 1e-2).bfloat16().to(DEV), (torch.randn(V, 1000, generator=g) * 0.02).bfloat16().to(DEV))
+                  for V in (136, 72, 264)]
+        out = rs.run(2, ragged)
+        assert out.shape == (BT, 1000)
+        assert torch.equal(out.view(torch.int16), K.dgrad_sum(ragged).view(torch.int16))
     torch.cuda.synchronize()
     dev = torch.device(DEV, torch.cuda.current_device())
     assert _lib.read_status(dev) == 0

@@ -239,3 +239,45 @@ def test_incomplete_group_is_flushed_by_the_next_pre_step():
     mgr.pre_step(lr=1e-2)                                # flushes what the last pass left
     torch.cuda.synchronize()
     assert not torch.equal(model["a"].weight.data, w_a)
+
+
+def test_group_with_members_on_both_autograd_paths_launches_inside_the_backward():
+    """One member of a group runs its backward in the Python autograd function (here: called directly,
+    as the tensor-parallel layers with a fused scatter do) and the others in the C++ node: the group
+    still goes out as soon as its last member has reported -- nothing is left for ``pre_step`` -- and
+    the weights equal those of ungrouped launches bit for bit."""
+    from forge_b200 import native
+    from forge_b200.autograd import FusedLinearFunction
+    torch.manual_seed(0)
+    base = nn.ModuleDict({k: nn.Linear(128, 192, bias=False) for k in ("a", "b", "c")}).to(DEV).bfloat16()
+    runs = []
+    for grouped in (False, True):
+        m = nn.ModuleDict({k: nn.Linear(128, 192, bias=False) for k in ("a", "b", "c")}).to(DEV).bfloat16()
+        m.load_state_dict(base.state_dict())
+        m = _fuse(m, "int8").train()
+        mgr = FusedOptimizerManager(m)
+        if grouped:
+            mgr.group_updates([[m["a"], m["b"], m["c"]]])
+        runs.append((m, mgr))
+    gen = torch.Generator(device=DEV).manual_seed(2)
+    for step in range(3):
+        x = torch.randn(64, 128, device=DEV, generator=gen).bfloat16()
+        for m, mgr in runs:
+            mgr.pre_step(lr=1e-2)
+            b = m["b"]
+            b._ensure_state()
+            yb = FusedLinearFunction.apply(x, b.weight, None, b._state, b._config, False, None, True, b._update_group)
+            ya, yc = m["a"](x), m["c"](x)
+            if native.module() is not None:
+                assert "CppNode" in ya.grad_fn.name() and "CppNode" not in yb.grad_fn.name()
+            (ya + yb + yc).float().square().mean().backward()
+            for g in mgr._update_groups:
+                assert g.pending() == 0, "the group was complete at the end of the backward pass"
+    torch.cuda.synchronize()
+    (m0, _), (m1, _) = runs
+    for k in ("a", "b", "c"):
+        assert torch.equal(_bits(m0[k].weight.data), _bits(m1[k].weight.data)), k
+        s0, s1 = m0[k].get_optimizer_state_dict(), m1[k].get_optimizer_state_dict()
+        for key, val in s0.items():
+            if torch.is_tensor(val):
+                assert torch.equal(_bits(val), _bits(s1[key])), f"{k}.{key}"

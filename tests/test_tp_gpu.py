@@ -68,6 +68,8 @@ def _worker(rank, world, port, mode, q):
         dist.destroy_process_group()
     except Exception as e:  # pragma: no cover
         q.put((rank, f"{type(e).__name__}: {e}"))
+        q.close()
+        q.join_thread()  # the message is on its way before the process goes
         os._exit(1)      # do not wait for a peer that is blocked in a collective
 
 
@@ -140,6 +142,8 @@ def _scatter_worker(rank, world, port, q):
     except Exception as e:  # pragma: no cover
         import traceback
         q.put((rank, f"{type(e).__name__}: {e} {traceback.format_exc()[-800:]}"))
+        q.close()
+        q.join_thread()
         os._exit(1)
 
 
@@ -219,6 +223,8 @@ def _module_scatter_worker(rank, world, port, q):
     except Exception as e:  # pragma: no cover
         import traceback
         q.put((rank, f"{type(e).__name__}: {e} {traceback.format_exc()[-800:]}"))
+        q.close()
+        q.join_thread()
         os._exit(1)
 
 
@@ -232,6 +238,107 @@ def test_two_rank_sharded_linear_with_fused_scatter():
     q = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_module_scatter_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = []
+    try:
+        for _ in procs:
+            out.append(q.get(timeout=150))
+            if out[-1][1] != "ok":
+                break
+    except Exception:
+        out.append(("parent", "timed out waiting for the ranks"))
+    for p in procs:
+        p.join(timeout=20)
+        if p.is_alive():
+            p.terminate()
+    assert sorted(out) == [(0, "ok"), (1, "ok")], out
+
+
+def _set_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=60))
+    try:
+        from forge_b200 import _lib
+        from forge_b200.peer import DgradReduceScatter
+        from forge_b200.tensor_parallel import RowShardedFusedLinear, RowShardedLinearSet
+        BT, H = 200, 528                              # ragged in both directions; H does not split into 128s
+        Vs = (776, 264, 264)
+        g = torch.Generator().manual_seed(3)
+        w0 = [(torch.randn(V, H, generator=g) * 0.05).bfloat16() for V in Vs]
+
+        def make():
+            return [RowShardedFusedLinear.from_full_weight(w.to(dev), gather_input=False, optimizer_type="adamw",
+                                                           state_mode="bf16").train() for w in w0]
+        plain, members = make(), make()
+        fused = RowShardedLinearSet(members)
+        rs = DgradReduceScatter([(BT, H, "allreduce")], device=dev)
+        fused.attach_fused_scatter(rs, 0)
+        for step in range(3):
+            x = torch.randn(BT, H, generator=g).bfloat16()
+            gys = [(torch.randn(BT, V, generator=g) * 1e-2).bfloat16() for V in Vs]
+            for layer in plain + members:
+                layer.local.update_optimizer_config(lr=1e-2, weight_decay=0.01)
+            # library GEMMs, autograd's additions and an NCCL all-reduce
+            xin = x.to(dev).requires_grad_(True)
+            outs = [m(xin) for m in plain]
+            torch.autograd.backward(outs, [gy[:, m.row_start:m.row_end].to(dev) for gy, m in zip(gys, plain)])
+            ref = xin.grad.clone()
+            dist.all_reduce(ref)
+            # one GEMM launch whose tiles go to both ranks
+            rs.begin_step()
+            xin2 = x.to(dev).requires_grad_(True)
+            outs2, complete = fused(xin2)
+            assert complete and "ShardedSetFusedAllReduce" in outs2[0].grad_fn.name()
+            for a, b in zip(outs, outs2):
+                assert torch.equal(a, b)
+            torch.autograd.backward(outs2, [gy[:, m.row_start:m.row_end].to(dev) for gy, m in zip(gys, members)])
+            exact = sum(gy.double() @ w.double() for gy, w in zip(gys, w0)) if step == 0 else None
+            scale = ref.float().abs().max().item()
+            assert (ref.float() - xin2.grad.float()).abs().max().item() <= 2e-2 * scale + 1e-6
+            if exact is not None:
+                err = (xin2.grad.double().cpu() - exact).abs().max().item()
+                err_ref = (ref.double().cpu() - exact).abs().max().item()
+                assert err <= 2.0 * err_ref + 1e-4 * exact.abs().max().item(), (err, err_ref)
+            # both ranks hold the same sum, bit for bit (fixed order of addition)
+            mine = xin2.grad.clone()
+            other = mine.clone()
+            dist.broadcast(other, src=0)
+            assert torch.equal(mine.view(torch.int16), other.view(torch.int16))
+            dist.barrier()
+        for a, b in zip(plain, members):
+            assert torch.equal(a.local.weight.data.view(torch.int16), b.local.weight.data.view(torch.int16))
+            sa, sb = a.local.get_optimizer_state_dict(), b.local.get_optimizer_state_dict()
+            for k, v in sa.items():
+                if torch.is_tensor(v):
+                    assert torch.equal(v.view(torch.uint8), sb[k].view(torch.uint8)), k
+        torch.cuda.synchronize()
+        assert _lib.read_status(dev) == 0
+        dist.barrier()
+        q.put((rank, "ok"))
+        dist.destroy_process_group()
+    except Exception as e:  # pragma: no cover
+        import traceback
+        q.put((rank, f"{type(e).__name__}: {e} {traceback.format_exc()[-800:]}"))
+        q.close()
+        q.join_thread()
+        os._exit(1)
+
+
+def test_two_rank_linear_set_with_fused_all_reduce():
+    """Three sharded linears on one replicated input: one GEMM launch that accumulates over the members
+    and stores its tiles into both ranks' buffers, against three library GEMMs + NCCL all-reduce.  Same
+    outputs, weights and optimizer state bit for bit; the input gradient as close to the exact sum, and
+    identical on the two ranks."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_set_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
     out = []
