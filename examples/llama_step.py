@@ -78,6 +78,9 @@ def main():
     ap.add_argument("--fused-scatter", action="store_true",
                     help="--tp: the input gradients of o and down through this library's dX GEMM with the reduce-scatter "
                          "fused into its epilogue (peer stores) instead of a library GEMM + NCCL reduce-scatter")
+    ap.add_argument("--fused-gather", action="store_true",
+                    help="--tp: the outputs of o and down through this library's forward GEMM with the all-gathers of "
+                         "its input and of its output fused in (peer stores) instead of NCCL all-gathers around a library GEMM")
     ap.add_argument("--fused-scatter-sets", choices=("all", "gathered"), default="all",
                     help="--fused-scatter: 'gathered' keeps q/k/v and gate/up (replicated input) on library GEMMs + NCCL "
                          "all-reduce; 'all' also forms their input gradient with one GEMM launch per set whose tiles go to every rank")
@@ -204,6 +207,8 @@ def run_tp(args):
     model = TPDecoder(cfg, state_mode=args.state, device=dev).train()
     if args.fused_scatter and world > 1:
         model.use_fused_scatter(args.seq, replicated_sets=args.fused_scatter_sets == "all")
+    if args.fused_gather and world > 1:
+        model.use_fused_gather(args.seq)
     manager = FusedOptimizerManager(model)
     if not args.no_group:
         manager.group_updates("layer")
@@ -288,7 +293,8 @@ def run_tp(args):
             "peak_hbm_gb_per_rank": stats[1].item(), "first_loss": losses[0], "last_loss": losses[-1],
             "device_status": int(stats[2].item()), "cuda_graph": bool(graph is not None),
             "grouped_launches": not args.no_group, "forge_dgrad": bool(args.forge_dgrad),
-            "fused_scatter": (args.fused_scatter_sets if args.fused_scatter and world > 1 else False), "clocks": clocks,
+            "fused_scatter": (args.fused_scatter_sets if args.fused_scatter and world > 1 else False),
+            "fused_gather": bool(args.fused_gather and world > 1), "clocks": clocks,
             "timing": "CUDA events per step, median over steps, max over ranks",
             "data": "synthetic uniform tokens (same on every rank), random init"}))
     sys.stdout.flush()

@@ -179,8 +179,11 @@ class Block(nn.Module):
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.nq != self.nkv)
         a = a.transpose(1, 2).reshape(B, T, self.nq * self.hd)
         # (with a fused scatter attached, o and down gather their own input and return the scattered gradient)
-        o = self.o(a) if self.o.gather_input else self.o(_GatherForShardedLinear.apply(a, self.group))
-        h = h + _GatherIntoReplicated.apply(o, self.group)
+        if self.o.returns_full_output(a):        # fused gathers: sharded input in, full output out
+            h = h + self.o(a)
+        else:
+            o = self.o(a) if self.o.gather_input else self.o(_GatherForShardedLinear.apply(a, self.group))
+            h = h + _GatherIntoReplicated.apply(o, self.group)
         x = self.norm2(h)
         if self.gu_set.fused(x):
             (gate, up), _ = self.gu_set(x)
@@ -188,6 +191,8 @@ class Block(nn.Module):
             x = _ToShardedLinears.apply(x, self.group)
             gate, up = self.gate(x), self.up(x)
         t = F.silu(gate) * up
+        if self.down.returns_full_output(t):
+            return h + self.down(t)
         d = self.down(t) if self.down.gather_input else self.down(_GatherForShardedLinear.apply(t, self.group))
         return h + _GatherIntoReplicated.apply(d, self.group)
 
@@ -242,6 +247,19 @@ class TPDecoder(nn.Module):
             lin.attach_fused_scatter(self.fused_scatter, i)
         return self
 
+    def use_fused_gather(self, tokens: int):
+        """Form the outputs of o and down with both all-gathers (of the feature-sharded input and of the
+        row-sharded output) fused into this library's forward GEMM (``forge_b200.peer.GatheredLinear``)
+        instead of NCCL all-gather + library GEMM + NCCL all-gather.  Collective."""
+        from forge_b200.peer import GatheredLinear
+        layers = [lin for blk in self.layers for lin in (blk.o, blk.down)]
+        self.fused_gather = GatheredLinear([(tokens, lin.in_features, lin.out_features) for lin in layers],
+                                           group=self.group, device=self.embed.weight.device)
+        for i, lin in enumerate(layers):
+            lin.gather_input = True
+            lin.attach_fused_gather(self.fused_gather, i)
+        return self
+
     def head_sharded_norm_params(self):
         """Replicated parameters whose gradients are partial sums per rank (per-head q / k norms)."""
         return [p for blk in self.layers if blk.qk_norm for p in (blk.q_norm.weight, blk.k_norm.weight)]
@@ -255,6 +273,8 @@ class TPDecoder(nn.Module):
         cos, sin = ang.cos().to(self.embed.weight.dtype), ang.sin().to(self.embed.weight.dtype)
         if getattr(self, "fused_scatter", None) is not None and self.training:
             self.fused_scatter.begin_step()      # this step's arrivals are told from the last one's by the epoch
+        if getattr(self, "fused_gather", None) is not None and self.training:
+            self.fused_gather.begin_step()
         h = self.embed(ids)
         for blk in self.layers:
             h = blk(h, cos, sin)

@@ -102,6 +102,16 @@ class ForgeDgradScatterArgs(ctypes.Structure):
                 ("all_ranks", ctypes.c_int32)]
 
 
+class ForgeLinearGatheredArgs(ctypes.Structure):
+    _fields_ = [("X", ctypes.c_void_p), ("W", ctypes.c_void_p), ("BT", ctypes.c_int64), ("H", ctypes.c_int64),
+                ("V_r", ctypes.c_int64), ("ld_x", ctypes.c_int64), ("ld_w", ctypes.c_int64),
+                ("x_arrivals", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("rank", ctypes.c_int32),
+                ("world", ctypes.c_int32), ("y", ctypes.c_void_p), ("ld_y", ctypes.c_int64),
+                ("y_dst", ctypes.POINTER(ctypes.c_void_p)), ("y_col", ctypes.c_int64), ("y_pitch", ctypes.c_int64),
+                ("y_arrivals", ctypes.POINTER(ctypes.c_void_p)), ("y_counter", ctypes.c_void_p),
+                ("status", ctypes.c_void_p)]
+
+
 class ForgeOptimArgs(ctypes.Structure):
     _fields_ = [
         ("grad", ctypes.c_void_p),
@@ -135,6 +145,14 @@ _SIGNATURES = {
     "forge_reduce_slots": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int64] * 3 + [ctypes.c_int32, ctypes.c_void_p,
                                                                                         ctypes.c_void_p]),
     "forge_set_arrival_wait_ns": (ctypes.c_int, [ctypes.c_uint64]),
+    "forge_push_block": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                        ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64, ctypes.c_int64,
+                                        ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
+                                        ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+    "forge_linear_gathered": (ctypes.c_int, [ctypes.POINTER(ForgeLinearGatheredArgs), ctypes.c_void_p]),
+    "forge_collect": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                     ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p,
+                                     ctypes.c_void_p]),
     "forge_rmsnorm_forward": (ctypes.c_int, [ctypes.c_void_p] * 3 + [ctypes.c_int64] * 4 + [ctypes.c_double, ctypes.c_void_p]),
     "forge_rmsnorm_backward": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int32] * 2 + [ctypes.c_int64] * 5
                                + [ctypes.c_double, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),

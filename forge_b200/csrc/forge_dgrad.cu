@@ -23,6 +23,13 @@
 //     (st.release.sys).  forge_reduce_slots on the owner waits (bounded) for all `world` arrival words and
 //     adds the slots in rank order in fp32.  This replaces GEMM -> NCCL reduce-scatter
 //     (src/fused_grad_optimizer/autograd.py:55 followed by a collective the reference does not have).
+//   * FWD: the forward product of the same mode, Y = X W_r^T (src/fused_grad_optimizer/autograd.py:34) with
+//     the all-gather of X fused into its consumer.  B = W_r is K-major here (H contiguous).  X arrives as
+//     `world` feature blocks that the ranks push into this rank's gathered buffer (forge_push_block); each
+//     block is one K segment, the own block first, and the producer waits (bounded) for a block's arrival
+//     word only when it reaches that segment, so the MMAs on the blocks that are there overlap the
+//     transfer of those that are not.  With the peer-store epilogue the output tiles go to every rank's
+//     gathered Y (the all-gather of the row-sharded output), otherwise to local memory by TMA.
 #include <cuda_bf16.h>
 #include <string.h>
 
@@ -47,7 +54,8 @@ constexpr int SMEM_BYTES = CTRL_BYTES + 1024 + STAGES * STAGE_BYTES + OUT_BYTES;
 constexpr int THREADS = 256;
 constexpr int ACC_BUFS = 4;
 constexpr int TMEM_COLS = 512;
-constexpr int MAX_SEG = 4;     // (dY_i, W_i) pairs accumulated into one dX
+constexpr int MAX_SEG = 8;     // K segments: (dY_i, W_i) pairs accumulated into one dX (four at most through the C
+                               // ABI), or the feature blocks of a gathered X
 constexpr int MAX_RANKS = 8;
 enum : int { ERR_OP_EMPTY = 201, ERR_OP_FULL = 202, ERR_ACC_EMPTY = 203, ERR_ACC_FULL = 204, ERR_ARRIVAL = 211 };
 
@@ -74,6 +82,11 @@ struct Params {
   // SCATTER
   int rank, world, block_cols;                 // block_cols = N / world, a multiple of BN
   int all_ranks;                               // 1: every tile goes to EVERY rank (slots are full width): a fused all-reduce
+                                               // 2: every tile goes to every rank's ONE gathered matrix, at column
+                                               //    push_col + n of rows push_pitch wide: an all-gather of the output
+  int push_pitch, push_col;
+  const uint32_t* seg_arrival[MAX_SEG];        // FWD: local arrival word of the block behind segment i, or NULL
+  unsigned long long wait_ns;                  // FWD: how long the producer waits for a block
   uint8_t* slots[MAX_RANKS];                   // receive buffer of every rank, (world, M, block_cols) bf16
   uint32_t* arrivals[MAX_RANKS];               // arrival words of every rank, `world` each; [rank] is written here
   uint32_t* counter;                           // local: CTAs of this launch that have finished
@@ -82,7 +95,7 @@ struct Params {
 };
 }  // namespace dg
 
-template <bool SCATTER>
+template <bool SCATTER, bool FWD>
 __global__ void __launch_bounds__(dg::THREADS, 1)
 forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ dg::Params p) {
   using namespace dg;
@@ -120,6 +133,7 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
       const uint64_t pol_a = policy_evict_last();    // dY is re-read by every column tile
       const uint64_t pol_b = policy_evict_first();   // W streams through once per row of tiles
       uint32_t it = 0;
+      uint32_t arrived = 0;                          // FWD: segments whose block is known to be here
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
         // consecutive CTAs share a column panel of W: tile index runs over M fastest
         const int m0 = (tile % p.tiles_m) * BM;
@@ -128,6 +142,25 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
           const CUtensorMap* tm_a = &p.seg[sg].tm_a;
           const CUtensorMap* tm_b = &p.seg[sg].tm_b;
           const int nkb = p.seg[sg].num_kb;
+          if constexpr (FWD) {
+            const uint32_t* aw = p.seg_arrival[sg];
+            if (aw != nullptr && !((arrived >> sg) & 1u)) {
+              const uint32_t e = *p.epoch;
+              const uint64_t t0 = global_timer_ns();
+              for (uint32_t i = 0;; ++i) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(aw) : "memory");
+                if (v == e) break;
+                if ((i & 15u) == 15u && (*abort_word != 0 || global_timer_ns() - t0 > p.wait_ns)) {
+                  atomicCAS(const_cast<int*>(abort_word), 0, ERR_ARRIVAL);
+                  goto done;
+                }
+                __nanosleep(64);
+              }
+              fence_proxy_async_global();
+              arrived |= 1u << sg;
+            }
+          }
           for (int kb = 0; kb < nkb; ++kb, ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1;
@@ -137,15 +170,19 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
             mbar_expect_tx(&ctrl->full[s], STAGE_BYTES);
             // rows / columns past the end of a segment are zero-filled and add nothing
             tma_load_2d(a, tm_a, &ctrl->full[s], kb * BK, m0, pol_a);
-            tma_load_2d(b, tm_b, &ctrl->full[s], n0, kb * BK, pol_b);
-            tma_load_2d(b + B_SLAB, tm_b, &ctrl->full[s], n0 + 64, kb * BK, pol_b);
+            if constexpr (FWD) {
+              tma_load_2d(b, tm_b, &ctrl->full[s], kb * BK, n0, pol_b);          // 128 rows of W_r, K-major
+            } else {
+              tma_load_2d(b, tm_b, &ctrl->full[s], n0, kb * BK, pol_b);
+              tma_load_2d(b + B_SLAB, tm_b, &ctrl->full[s], n0 + 64, kb * BK, pol_b);
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, false, true);
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, false, !FWD);
       uint32_t it = 0, tile_it = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_it) {
         const int buf = tile_it % ACC_BUFS;
@@ -166,7 +203,9 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
             // of M are 1024 bytes apart.  B (N-major): 16 K-rows further = two 1024-byte atoms;
             // 64-column slabs are B_SLAB bytes apart.
             const uint64_t da = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
-            const uint64_t db = make_smem_desc_sw128(b_addr + k * 2048, B_SLAB, 1024);
+            // FWD: B is K-major like A (128 rows of W_r, 8-row groups 1024 bytes apart)
+            const uint64_t db = FWD ? make_smem_desc_sw128(b_addr + k * 32, 16, 1024)
+                                    : make_smem_desc_sw128(b_addr + k * 2048, B_SLAB, 1024);
             umma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&ctrl->empty[s]);
@@ -238,12 +277,14 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
         // instruction, sixteen lanes x 16 bytes = one 256-byte run per row.
         // (all_ranks: the tile goes to every rank's slot [this rank], which is then N columns wide)
         const int piece = lane & 15, bx = piece >> 3, pc = piece & 7;
+        // (all_ranks == 2: to every rank's single gathered matrix, at this rank's column offset)
         const int first = p.all_ranks ? 0 : n0 / p.block_cols;
         const int last = p.all_ranks ? p.world - 1 : first;
-        const int pitch = p.all_ranks ? p.N : p.block_cols;          // columns of a slot row
-        const int col = p.all_ranks ? n0 : n0 - first * p.block_cols;
+        const int pitch = p.all_ranks == 2 ? p.push_pitch : p.all_ranks ? p.N : p.block_cols;     // columns of a slot row
+        const int col = p.all_ranks == 2 ? p.push_col + n0 : p.all_ranks ? n0 : n0 - first * p.block_cols;
+        const size_t slot_row0 = p.all_ranks == 2 ? 0 : static_cast<size_t>(p.rank) * p.M;
         for (int owner = first; owner <= last; ++owner) {
-          uint8_t* dst = p.slots[owner] + (static_cast<size_t>(p.rank) * p.M * pitch + col) * 2;
+          uint8_t* dst = p.slots[owner] + (slot_row0 * pitch + col) * 2;
 #pragma unroll 4
           for (int rr = 0; rr < 32; rr += 2) {
             const int row = quarter * 32 + rr + (lane >> 4);
@@ -301,7 +342,9 @@ done:
 __global__ void __launch_bounds__(256)
 forge_reduce_slots_kernel(const uint8_t* __restrict__ slots, const uint32_t* arrivals, const uint32_t* epoch,
                           __nv_bfloat16* __restrict__ out, int M, int S, long long ld_out, int world, int* status,
-                          unsigned long long limit_ns) {
+                          unsigned long long limit_ns, int n_slots, long long ld_slot) {
+  // n_slots = world, ld_slot = S: the sum of the ranks' slots.  n_slots = 1: a copy of one gathered
+  // matrix (row pitch ld_slot) once all `world` arrival words are there.
   __shared__ int ok;
   if (threadIdx.x == 0) {
     const uint32_t e = *epoch;
@@ -323,13 +366,13 @@ forge_reduce_slots_kernel(const uint8_t* __restrict__ slots, const uint32_t* arr
   if (!ok) return;
   const long long pieces_per_row = S / 8;
   const long long total = static_cast<long long>(M) * pieces_per_row;
-  const size_t slot_bytes = static_cast<size_t>(M) * S * 2;
+  const size_t slot_bytes = static_cast<size_t>(M) * ld_slot * 2;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long m = i / pieces_per_row, pc = i - m * pieces_per_row;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int src = 0; src < world; ++src) {
-      const uint4 q = *reinterpret_cast<const uint4*>(slots + src * slot_bytes + (m * S + pc * 8) * 2);
+    for (int src = 0; src < n_slots; ++src) {
+      const uint4 q = *reinterpret_cast<const uint4*>(slots + src * slot_bytes + (m * ld_slot + pc * 8) * 2);
       const uint32_t u[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -351,12 +394,12 @@ using namespace forge;
 namespace {
 
 // validation, tensor maps of the segments and launch shared by the two entry points
-template <bool SCATTER>
+template <bool SCATTER, bool FWD = false>
 int launch_dgrad(const ForgeDgradSegment* segs, int nseg, void* dX, int64_t BT, int64_t H, int64_t ld_dx, dg::Params& p,
                  int32_t* status, cudaStream_t stream) {
   using namespace forge::dg;
   if (BT < 0 || H < 0 || nseg < 0) return fail(FORGE_ERR_INVALID_ARG, "negative dimension");
-  if (nseg > MAX_SEG) return fail(FORGE_ERR_INVALID_ARG, "at most %d (dY, W) pairs per launch (got %d)", MAX_SEG, nseg);
+  if (nseg > (FWD ? MAX_SEG : 4)) return fail(FORGE_ERR_INVALID_ARG, "at most %d K segments per launch (got %d)", FWD ? MAX_SEG : 4, nseg);
   if (BT == 0 || H == 0) return FORGE_OK;
   if (nseg > 0 && segs == nullptr) return fail(FORGE_ERR_INVALID_ARG, "segments pointer is NULL");
   if (BT > (1 << 28) || H > (1ll << 30)) return fail(FORGE_ERR_SHAPE, "dimension too large");
@@ -382,9 +425,14 @@ int launch_dgrad(const ForgeDgradSegment* segs, int nseg, void* dX, int64_t BT, 
     if (g.V < 0 || g.V > (1ll << 30)) return fail(FORGE_ERR_INVALID_ARG, "segment %d: bad V", i);
     if (g.V == 0) continue;
     if (g.dY == nullptr || g.W == nullptr) return fail(FORGE_ERR_INVALID_ARG, "segment %d: null pointer", i);
+    p.seg_arrival[p.nseg] = p.seg_arrival[i];      // (FWD) follows its segment when empty ones are dropped
     Segment& sg = p.seg[p.nseg++];
     if ((rc = encode_tmap_2d(&sg.tm_a, g.dY, 2, true, BT, g.V, g.ld_dy, BK, BM, 128)) != FORGE_OK) return rc;
-    if ((rc = encode_tmap_2d(&sg.tm_b, g.W, 2, true, g.V, H, g.ld_w, 64, BK, 128)) != FORGE_OK) return rc;
+    if (FWD) {   // W_r block: H rows (the output columns) of g.V contiguous K elements
+      if ((rc = encode_tmap_2d(&sg.tm_b, g.W, 2, true, H, g.V, g.ld_w, BK, BN, 128)) != FORGE_OK) return rc;
+    } else {
+      if ((rc = encode_tmap_2d(&sg.tm_b, g.W, 2, true, g.V, H, g.ld_w, 64, BK, 128)) != FORGE_OK) return rc;
+    }
     sg.num_kb = static_cast<int>((g.V + BK - 1) / BK);
     p.total_kb += sg.num_kb;
   }
@@ -393,7 +441,7 @@ int launch_dgrad(const ForgeDgradSegment* segs, int nseg, void* dX, int64_t BT, 
     p.seg[0].tm_b = tm_out;
     p.seg[0].num_kb = 0;
   }
-  auto kern = forge_dgrad_kernel<SCATTER>;
+  auto kern = forge_dgrad_kernel<SCATTER, FWD>;
   static std::atomic<bool> attr_set[64];   // per device: the shared-memory opt-in has been made
   int dev = 0;
   cudaGetDevice(&dev);
@@ -477,8 +525,158 @@ extern "C" int forge_reduce_slots(const void* slots, const uint32_t* arrivals, c
   const int grid = static_cast<int>(std::min<int64_t>((pieces + 255) / 256, 2 * di->sm_count));
   forge_reduce_slots_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
       static_cast<const uint8_t*>(slots), arrivals, epoch, static_cast<__nv_bfloat16*>(out), static_cast<int>(BT),
-      static_cast<int>(block_cols), ld_out, world, status, g_arrival_wait_ns.load());
+      static_cast<int>(block_cols), ld_out, world, status, g_arrival_wait_ns.load(), world, block_cols);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "reduce kernel launch: %s", cudaGetErrorString(e));
   return FORGE_OK;
+}
+
+extern "C" int forge_collect(const void* gathered, int64_t ld_gathered, const uint32_t* arrivals, const uint32_t* epoch,
+                             void* out, int64_t BT, int64_t cols, int64_t ld_out, int32_t world, int32_t* status,
+                             void* cuda_stream) {
+  if (gathered == nullptr || arrivals == nullptr || epoch == nullptr || out == nullptr)
+    return fail(FORGE_ERR_INVALID_ARG, "forge_collect: null pointer");
+  if (world < 1 || world > dg::MAX_RANKS || BT < 0 || cols <= 0 || cols % 8 != 0 || ld_out % 8 != 0 || ld_gathered % 8 != 0 ||
+      ld_gathered < cols || !aligned16(gathered) || !aligned16(out))
+    return fail(FORGE_ERR_INVALID_ARG, "forge_collect: bad shape, world size or alignment");
+  if (BT == 0) return FORGE_OK;
+  const DeviceInfo* di = current_device_info();
+  if (di == nullptr) return FORGE_ERR_CUDA;
+  const int64_t pieces = BT * (cols / 8);
+  const int grid = static_cast<int>(std::min<int64_t>((pieces + 255) / 256, 2 * di->sm_count));
+  forge_reduce_slots_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint8_t*>(gathered), arrivals, epoch, static_cast<__nv_bfloat16*>(out), static_cast<int>(BT),
+      static_cast<int>(cols), ld_out, world, status, g_arrival_wait_ns.load(), 1, ld_gathered);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "collect kernel launch: %s", cudaGetErrorString(e));
+  return FORGE_OK;
+}
+
+namespace forge {
+// this rank's (M, cols) block -> column `col` of every rank's (M, ld_dst) matrix; the last CTA raises
+// arrival word [rank] on every rank (same protocol as the GEMM's peer-store epilogue)
+struct PushParams {
+  const uint8_t* src;
+  long long ld_src, ld_dst, col;
+  int M, cols, rank, world;
+  uint8_t* dst[dg::MAX_RANKS];
+  uint32_t* arrivals[dg::MAX_RANKS];
+  uint32_t* counter;
+  const uint32_t* epoch;
+};
+
+__global__ void __launch_bounds__(256)
+forge_push_block_kernel(const __grid_constant__ PushParams p) {
+  const long long pieces_per_row = p.cols / 8;
+  const long long total = static_cast<long long>(p.M) * pieces_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long m = i / pieces_per_row, pc = i - m * pieces_per_row;
+    const uint4 v = *reinterpret_cast<const uint4*>(p.src + (m * p.ld_src + pc * 8) * 2);
+    for (int o = 0; o < p.world; ++o)
+      *reinterpret_cast<uint4*>(p.dst[o] + (m * p.ld_dst + p.col + pc * 8) * 2) = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t done = atomicAdd(p.counter, 1u);
+    if (done == gridDim.x - 1) {
+      __threadfence_system();
+      *p.counter = 0u;
+      const uint32_t e = *p.epoch;
+      for (int o = 0; o < p.world; ++o)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.arrivals[o] + p.rank), "r"(e) : "memory");
+    }
+  }
+}
+}  // namespace forge
+
+extern "C" int forge_push_block(const void* src, int64_t BT, int64_t cols, int64_t ld_src, void* const* dst, int64_t col,
+                                int64_t ld_dst, uint32_t* const* arrivals, uint32_t* counter, const uint32_t* epoch,
+                                int32_t rank, int32_t world, int32_t* status, void* cuda_stream) {
+  (void)status;
+  if (src == nullptr || dst == nullptr || arrivals == nullptr || counter == nullptr || epoch == nullptr)
+    return fail(FORGE_ERR_INVALID_ARG, "forge_push_block: null pointer");
+  if (world < 1 || world > dg::MAX_RANKS || rank < 0 || rank >= world)
+    return fail(FORGE_ERR_INVALID_ARG, "rank %d of %d (at most %d ranks)", rank, world, dg::MAX_RANKS);
+  if (BT < 0 || cols <= 0 || cols % 8 != 0 || col < 0 || col % 8 != 0 || ld_src % 8 != 0 || ld_dst % 8 != 0 ||
+      col + cols > ld_dst || ld_src < cols || !aligned16(src))
+    return fail(FORGE_ERR_INVALID_ARG, "forge_push_block: bad shape or alignment");
+  forge::PushParams p;
+  memset(&p, 0, sizeof(p));
+  for (int r = 0; r < world; ++r) {
+    if (dst[r] == nullptr || arrivals[r] == nullptr || !aligned16(dst[r]))
+      return fail(FORGE_ERR_INVALID_ARG, "gathered matrix or arrival words of rank %d are NULL or misaligned", r);
+    p.dst[r] = static_cast<uint8_t*>(dst[r]);
+    p.arrivals[r] = arrivals[r];
+  }
+  if (BT == 0) return FORGE_OK;
+  const DeviceInfo* di = current_device_info();
+  if (di == nullptr) return FORGE_ERR_CUDA;
+  p.src = static_cast<const uint8_t*>(src);
+  p.ld_src = ld_src;
+  p.ld_dst = ld_dst;
+  p.col = col;
+  p.M = static_cast<int>(BT);
+  p.cols = static_cast<int>(cols);
+  p.rank = rank;
+  p.world = world;
+  p.counter = counter;
+  p.epoch = epoch;
+  const int64_t pieces = BT * (cols / 8);
+  const int grid = static_cast<int>(std::min<int64_t>((pieces + 255) / 256, di->sm_count));
+  forge::forge_push_block_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "push kernel launch: %s", cudaGetErrorString(e));
+  return FORGE_OK;
+}
+
+extern "C" int forge_linear_gathered(const ForgeLinearGatheredArgs* args, void* cuda_stream) {
+  using namespace forge::dg;
+  if (args == nullptr) return fail(FORGE_ERR_INVALID_ARG, "forge_linear_gathered: args is NULL");
+  const ForgeLinearGatheredArgs& a = *args;
+  if (a.world < 1 || a.world > MAX_RANKS || a.rank < 0 || a.rank >= a.world)
+    return fail(FORGE_ERR_INVALID_ARG, "rank %d of %d (at most %d ranks)", a.rank, a.world, MAX_RANKS);
+  if (a.X == nullptr || a.W == nullptr || a.epoch == nullptr)
+    return fail(FORGE_ERR_INVALID_ARG, "forge_linear_gathered: X / W / epoch is NULL");
+  if (a.H <= 0 || a.H % (8 * a.world) != 0)
+    return fail(FORGE_ERR_SHAPE, "H (%lld) must split into %d feature blocks that are multiples of 8 columns", (long long)a.H, a.world);
+  if (a.V_r < 0 || a.V_r % 8 != 0) return fail(FORGE_ERR_SHAPE, "V_r (%lld) must be a multiple of 8", (long long)a.V_r);
+  const int64_t blk = a.H / a.world;
+  Params p;
+  memset(&p, 0, sizeof(p));
+  p.rank = a.rank;
+  p.world = a.world;
+  p.epoch = a.epoch;
+  p.wait_ns = g_arrival_wait_ns.load();
+  // K segments = feature blocks, the own block first, then the ranks after this one in ring order
+  ForgeDgradSegment segs[MAX_SEG];
+  for (int i = 0; i < a.world; ++i) {
+    const int src = (a.rank + i) % a.world;
+    segs[i].dY = static_cast<const uint8_t*>(a.X) + src * blk * 2;
+    segs[i].W = static_cast<const uint8_t*>(a.W) + src * blk * 2;
+    segs[i].V = blk;
+    segs[i].ld_dy = a.ld_x;
+    segs[i].ld_w = a.ld_w;
+    p.seg_arrival[i] = (a.x_arrivals != nullptr && src != a.rank) ? a.x_arrivals + src : nullptr;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (a.y != nullptr)
+    return launch_dgrad<false, true>(segs, a.world, a.y, a.BT, a.V_r, a.ld_y, p, a.status, stream);
+  if (a.y_dst == nullptr || a.y_arrivals == nullptr || a.y_counter == nullptr)
+    return fail(FORGE_ERR_INVALID_ARG, "forge_linear_gathered: neither a local output nor the pushed form's buffers");
+  if (a.y_col < 0 || a.y_col % 8 != 0 || a.y_pitch % 8 != 0 || a.y_col + a.V_r > a.y_pitch)
+    return fail(FORGE_ERR_SHAPE, "pushed output: column offset / pitch must be multiples of 8 and hold V_r columns");
+  for (int r = 0; r < a.world; ++r) {
+    if (a.y_dst[r] == nullptr || a.y_arrivals[r] == nullptr || !aligned16(a.y_dst[r]))
+      return fail(FORGE_ERR_INVALID_ARG, "gathered output or arrival words of rank %d are NULL or misaligned", r);
+    p.slots[r] = static_cast<uint8_t*>(a.y_dst[r]);
+    p.arrivals[r] = a.y_arrivals[r];
+  }
+  p.counter = a.y_counter;
+  p.all_ranks = 2;
+  p.push_pitch = static_cast<int>(a.y_pitch);
+  p.push_col = static_cast<int>(a.y_col);
+  p.block_cols = static_cast<int>(a.V_r);
+  return launch_dgrad<true, true>(segs, a.world, nullptr, a.BT, a.V_r, 0, p, a.status, stream);
 }

@@ -166,6 +166,12 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// order this thread's earlier (acquire) reads of global memory before its later bulk-tensor loads: data
+// another GPU wrote with ordinary stores and published with a release is then what the loads see
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // tcgen05: tensor memory + UMMA
 // ---------------------------------------------------------------------------------------------

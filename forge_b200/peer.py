@@ -144,3 +144,116 @@ class DgradReduceScatter:
                                               out.data_ptr(), bt, s, out.stride(0), self.world, status, stream),
                        "forge_reduce_slots")
         return out
+
+
+class GatheredLinear:
+    """The forward products of a step's feature-sharded-input linears (o, down), ``Y = gather(X) W_r^T``,
+    with both all-gathers of the row-sharded mode fused in (``forge_push_block`` / ``forge_linear_gathered``
+    / ``forge_collect``): every rank pushes its block of X into every rank's gathered input with plain
+    peer stores; the GEMM starts on the own block and waits for another block only when it reaches it;
+    its epilogue stores the output tiles into every rank's gathered output, which a small kernel copies
+    out once all ranks have arrived.  No reference counterpart (``F.linear``, ``autograd.py:34``).
+
+    ``sets``: one ``(BT, H, V)`` per linear (full sizes).  ``begin_step()`` advances the epoch and runs one
+    tiny collective: a buffer of the step before may be rewritten only when every rank has finished
+    with it, and a collective on the stream after that step's work is what shows it.  The gathered input
+    of a set stays valid until the next ``begin_step`` (the backward pass reads it).  Collective
+    constructor; at most 8 ranks.
+    """
+
+    def __init__(self, sets, group=None, device=None):
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.sets = [(int(bt), int(h), int(v)) for bt, h, v in sets]
+        for bt, h, v in self.sets:
+            if h % (8 * self.world) or v % (8 * self.world):
+                raise ValueError(f"H ({h}) and V ({v}) must split into {self.world} blocks that are multiples of 8")
+        xo, yo, total_x, total_y = [], [], 0, 0
+        for bt, h, v in self.sets:
+            xo.append(total_x)
+            yo.append(total_y)
+            total_x += (bt * h * 2 + 255) // 256 * 256
+            total_y += (bt * v * 2 + 255) // 256 * 256
+        self._x_off, self._y_off = xo, yo
+        n = len(self.sets)
+        self.x_buf = torch.zeros(max(total_x, 256), dtype=torch.uint8, device=self.device)
+        self.y_buf = torch.zeros(max(total_y, 256), dtype=torch.uint8, device=self.device)
+        # per set: `world` arrival words for the input blocks, `world` for the output blocks
+        self.arrivals = torch.zeros(max(2 * n * self.world, 1), dtype=torch.int32, device=self.device)
+        self.counters = torch.zeros(max(2 * n, 1), dtype=torch.int32, device=self.device)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.tick = torch.zeros(1, dtype=torch.float32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        px, py, pa = _share(self.x_buf, group), _share(self.y_buf, group), _share(self.arrivals, group)
+        self._keep = (px, py, pa)
+        w = self.world
+        arr = ctypes.c_void_p * w
+        self._x_dst = [arr(*[t.data_ptr() + xo[i] for t in px]) for i in range(n)]
+        self._y_dst = [arr(*[t.data_ptr() + yo[i] for t in py]) for i in range(n)]
+        self._x_arr = [arr(*[t.data_ptr() + 4 * (2 * i) * w for t in pa]) for i in range(n)]
+        self._y_arr = [arr(*[t.data_ptr() + 4 * (2 * i + 1) * w for t in pa]) for i in range(n)]
+        if self.world > 1:
+            dist.barrier(group=group)
+
+    def begin_step(self):
+        self.epoch.add_(1)
+        if self.world > 1:
+            dist.all_reduce(self.tick, group=self.group)
+
+    def gathered_input(self, index: int) -> torch.Tensor:
+        bt, h, _ = self.sets[index]
+        return self.x_buf[self._x_off[index]: self._x_off[index] + bt * h * 2].view(torch.bfloat16).view(bt, h)
+
+    def push(self, index: int, x_block: torch.Tensor):
+        """This rank's ``(BT, H / world)`` block of the input into every rank's gathered input."""
+        bt, h, _ = self.sets[index]
+        blk = h // self.world
+        if x_block.dtype != torch.bfloat16 or tuple(x_block.shape) != (bt, blk) or x_block.stride(1) != 1:
+            raise ValueError(f"expected a bf16 ({bt}, {blk}) block with contiguous rows")
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.forge_push_block(x_block.data_ptr(), bt, blk, x_block.stride(0), self._x_dst[index],
+                                            self.rank * blk, h, self._x_arr[index],
+                                            self.counters.data_ptr() + 4 * (2 * index), self.epoch.data_ptr(),
+                                            self.rank, self.world, _lib.status_word(self.device).data_ptr(),
+                                            _lib.current_stream_ptr(self.device)), "forge_push_block")
+
+    def linear(self, index: int, weight: torch.Tensor, full_output: bool = True) -> torch.Tensor:
+        """``gather(X) W_r^T`` for the set's pushed input; ``weight``: this rank's ``(V / world, H)`` rows.
+        ``full_output``: the ``(BT, V)`` output gathered over the ranks (every rank gets the same), else this
+        rank's ``(BT, V / world)`` columns."""
+        bt, h, v = self.sets[index]
+        vr = v // self.world
+        if weight.dtype != torch.bfloat16 or tuple(weight.shape) != (vr, h) or weight.stride(1) != 1:
+            raise ValueError(f"expected this rank's bf16 ({vr}, {h}) rows of the weight")
+        a = _lib.ForgeLinearGatheredArgs()
+        a.X = self.x_buf.data_ptr() + self._x_off[index]
+        a.W = weight.data_ptr()
+        a.BT, a.H, a.V_r, a.ld_x, a.ld_w = bt, h, vr, h, weight.stride(0)
+        a.x_arrivals = self.arrivals.data_ptr() + 4 * (2 * index) * self.world
+        a.epoch = self.epoch.data_ptr()
+        a.rank, a.world = self.rank, self.world
+        status = _lib.status_word(self.device).data_ptr()
+        a.status = status
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            stream = _lib.current_stream_ptr(self.device)
+            if not full_output:
+                out = torch.empty(bt, vr, dtype=torch.bfloat16, device=self.device)
+                a.y, a.ld_y = out.data_ptr(), vr
+                _lib.check(lib.forge_linear_gathered(ctypes.byref(a), stream), "forge_linear_gathered")
+                return out
+            a.y = None
+            a.y_dst, a.y_col, a.y_pitch = self._y_dst[index], self.rank * vr, v
+            a.y_arrivals = self._y_arr[index]
+            a.y_counter = self.counters.data_ptr() + 4 * (2 * index + 1)
+            _lib.check(lib.forge_linear_gathered(ctypes.byref(a), stream), "forge_linear_gathered")
+            out = torch.empty(bt, v, dtype=torch.bfloat16, device=self.device)
+            _lib.check(lib.forge_collect(self.y_buf.data_ptr() + self._y_off[index], v,
+                                         self.arrivals.data_ptr() + 4 * (2 * index + 1) * self.world,
+                                         self.epoch.data_ptr(), out.data_ptr(), bt, v, v, self.world, status, stream),
+                       "forge_collect")
+        return out

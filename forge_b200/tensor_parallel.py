@@ -133,6 +133,47 @@ class _ShardedLinearFusedScatter(torch.autograd.Function):
         return dx_shard, None, None, None, None, None
 
 
+class _ShardedLinearFusedGather(torch.autograd.Function):
+    """A row-sharded linear on a feature-sharded input whose forward has both of its all-gathers fused in
+    (``forge_b200.peer.GatheredLinear``): the input block is pushed to every rank, the GEMM consumes the
+    blocks as they arrive and stores its output tiles into every rank's gathered output.  Input
+    ``(…, H / R)``, output the full ``(…, V)`` (the same on every rank).  Backward: this rank's columns
+    of the output gradient, then as ``_ShardedLinearFusedScatter`` (or library GEMM + NCCL
+    reduce-scatter when no fused scatter is attached)."""
+
+    @staticmethod
+    def forward(ctx, x_shard, weight, layer):
+        fwd, idx = layer._gather, layer._gather_index
+        x2d = x_shard.reshape(-1, x_shard.shape[-1])
+        if not x2d.is_contiguous():
+            x2d = x2d.contiguous()
+        fwd.push(idx, x2d)
+        y = fwd.linear(idx, weight.data, full_output=True)
+        # the gathered input lives in the set's buffer until the next step begins: the backward reads it there
+        ctx.save_for_backward(fwd.gathered_input(idx), weight)
+        ctx.layer, ctx.shard_shape = layer, x_shard.shape
+        return y.view(*x_shard.shape[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, grad_full):
+        from forge_b200.autograd import _apply_fused
+        x2d, weight = ctx.saved_tensors
+        layer = ctx.layer
+        local = layer.local
+        vr = weight.shape[0]
+        dy2d = grad_full.reshape(-1, grad_full.shape[-1])[:, layer.rank * vr:(layer.rank + 1) * vr].contiguous()
+        # before the in-place update of `weight` on this stream
+        if layer._scatter is not None:
+            dx_shard = layer._scatter.run(layer._scatter_index, [(dy2d, weight.data)])
+        else:
+            dx_shard = reduce_scatter_features(dy2d @ weight.data, layer.group)
+        if local._update_group is not None:
+            local._update_group.add(weight, lambda: _apply_fused(dy2d, x2d, weight, local._state, local._config))
+        else:
+            _apply_fused(dy2d, x2d, weight, local._state, local._config)
+        return dx_shard.view(ctx.shard_shape), None, None
+
+
 class _ShardedSetFusedAllReduce(torch.autograd.Function):
     """Several row-sharded linears on one REPLICATED input (q / k / v; gate / up).  Forward: one
     ``F.linear`` per member.  Backward: ONE launch of this library's dX GEMM accumulates
@@ -235,6 +276,8 @@ class RowShardedFusedLinear(nn.Module):
             self.local = FusedLinear(in_features, self.row_end - self.row_start, **fused_kwargs)
         if dtype is not None:
             self.local = self.local.to(dtype=dtype)
+        self._scatter, self._scatter_index = None, None      # see attach_fused_scatter
+        self._gather, self._gather_index = None, None        # see attach_fused_gather
 
     @classmethod
     def from_full_weight(cls, weight: torch.Tensor, rank=None, world=None, group=None, **kw):
@@ -255,15 +298,32 @@ class RowShardedFusedLinear(nn.Module):
         their input (``gather_input=True``) with bf16 weights and no bias."""
         self._scatter, self._scatter_index = scatter, index
 
-    def forward(self, x):
-        sc = getattr(self, "_scatter", None)
+    def attach_fused_gather(self, gather, index: int):
+        """Use ``gather`` (a ``forge_b200.peer.GatheredLinear``), set ``index``, for this layer's forward:
+        the all-gather of its input and of its output are fused into the GEMM.  The layer then takes the
+        feature-sharded input and returns the FULL ``(…, V)`` output (``returns_full_output``), so the
+        caller must not gather it again.  Same conditions as ``attach_fused_scatter``."""
+        self._gather, self._gather_index = gather, index
+
+    def _fused_conditions(self, x) -> bool:
         loc = self.local
-        if (sc is not None and self.gather_input and self.world > 1 and loc.training and loc._config is not None
+        if not (self.gather_input and self.world > 1 and loc.training and loc._config is not None
                 and not loc._is_accumulating and loc.use_fused_backward and loc.bias is None and x.is_cuda
                 and x.dtype == torch.bfloat16 and loc.weight.dtype == torch.bfloat16):
-            loc._ensure_state()
-            if loc._state._pending_grad is None:
-                return _ShardedLinearFusedScatter.apply(x, loc.weight, loc, sc, self._scatter_index, self.group)
+            return False
+        loc._ensure_state()
+        return loc._state._pending_grad is None
+
+    def returns_full_output(self, x) -> bool:
+        return self._gather is not None and self._fused_conditions(x)
+
+    def forward(self, x):
+        sc = self._scatter
+        loc = self.local
+        if self._gather is not None and self._fused_conditions(x):
+            return _ShardedLinearFusedGather.apply(x, loc.weight, self)
+        if sc is not None and self._fused_conditions(x):
+            return _ShardedLinearFusedScatter.apply(x, loc.weight, loc, sc, self._scatter_index, self.group)
         if self.gather_input and self.world > 1:
             x = _GatherX.apply(x, self.group)
         return self.local(x)

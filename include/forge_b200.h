@@ -251,6 +251,50 @@ int forge_reduce_slots(const void* slots, const uint32_t* arrivals, const uint32
  * process-wide; tests shorten it). */
 int forge_set_arrival_wait_ns(uint64_t ns);
 
+/* The forward product of the row-sharded mode with its all-gathers fused in (no counterpart in the
+ * reference: Y = X W^T is `F.linear`, src/fused_grad_optimizer/autograd.py:34, and it has no distributed
+ * code).  Three calls:
+ *
+ * forge_push_block: copies this rank's (BT, cols) bf16 block into EVERY rank's gathered (BT, ld_dst)
+ *   matrix at column `col` with plain peer stores, then sets arrival word [rank] on every rank to
+ *   *epoch.  dst[o], arrivals[o]: rank o's matrix and its `world` arrival words mapped into this
+ *   process; counter: a local zero word (left zero).  This is the all-gather of a feature-sharded X.
+ *
+ * forge_linear_gathered: Y = X W_r^T, X the gathered (BT, H) matrix in LOCAL memory that the ranks fill
+ *   with forge_push_block, cut into `world` equal feature blocks; W_r this rank's (V_r, H) rows.  The
+ *   GEMM starts with the own block and waits for each other block's arrival word (x_arrivals[src] ==
+ *   *epoch; bounded like every wait, code 211) only when it gets there.  x_arrivals == NULL: X is
+ *   complete already.  Output: y != NULL -> local (BT, V_r) bf16 with row pitch ld_y.  y == NULL -> every
+ *   tile is stored into EVERY rank's gathered (BT, y_pitch) output at column y_col (the all-gather of the
+ *   row-sharded output: y_dst[o], y_arrivals[o], y_counter as in forge_push_block), to be picked up with
+ *   forge_collect.  H / world must be a multiple of 8, y_col and y_pitch too.
+ *
+ * forge_collect: waits (bounded, code 211) until all `world` arrival words equal *epoch, then copies
+ *   the gathered (BT, cols) matrix to `out`. */
+int forge_push_block(const void* src, int64_t BT, int64_t cols, int64_t ld_src, void* const* dst, int64_t col,
+                     int64_t ld_dst, uint32_t* const* arrivals, uint32_t* counter, const uint32_t* epoch,
+                     int32_t rank, int32_t world, int32_t* status, void* cuda_stream);
+
+typedef struct ForgeLinearGatheredArgs {
+  const void* X;                 /* local gathered input (BT, H), row pitch ld_x */
+  const void* W;                 /* this rank's rows (V_r, H), row pitch ld_w */
+  int64_t BT, H, V_r, ld_x, ld_w;
+  const uint32_t* x_arrivals;    /* local: `world` words, or NULL */
+  const uint32_t* epoch;
+  int32_t rank, world;
+  void* y;                       /* local output, or NULL for the pushed form */
+  int64_t ld_y;
+  void* const* y_dst;            /* pushed form: every rank's gathered output, column offset and row pitch */
+  int64_t y_col, y_pitch;
+  uint32_t* const* y_arrivals;
+  uint32_t* y_counter;
+  int32_t* status;
+} ForgeLinearGatheredArgs;
+int forge_linear_gathered(const ForgeLinearGatheredArgs* args, void* cuda_stream);
+
+int forge_collect(const void* gathered, int64_t ld_gathered, const uint32_t* arrivals, const uint32_t* epoch, void* out,
+                  int64_t BT, int64_t cols, int64_t ld_out, int32_t world, int32_t* status, void* cuda_stream);
+
 /* RMSNorm recomputation for linears that fold their preceding norm (the normalised activation is not
  * kept between forward and backward): y = bf16(gamma * (x * rsqrt(mean(x^2) + eps))), fp32 inside;
  * x, gamma, y bf16; x and y (rows, H) row-major, H a multiple of 8 and at most 16384.  Replaces

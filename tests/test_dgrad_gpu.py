@@ -137,3 +137,43 @@ def test_scatter_and_reduce_on_one_rank_equal_the_plain_gemm():
         _lib.read_status(dev)
     if own_group:
         dist.destroy_process_group()
+
+
+def test_gathered_linear_on_one_rank_equals_the_plain_product():
+    """The forward GEMM of the row-sharded mode with a world of one: push of the (only) input block, the
+    K-major product, both output forms (local TMA store; peer-store epilogue + collect), ragged sizes."""
+    import torch.distributed as dist
+    from forge_b200 import _lib
+    from forge_b200.peer import GatheredLinear
+    own_group = not dist.is_initialized()
+    if own_group:
+        import socket
+        sock = socket.socket()
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+        sock.close()
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
+    g = torch.Generator().manual_seed(31)
+    dev = torch.device(DEV, torch.cuda.current_device())
+    sets = [(200, 1000, 264), (512, 4096, 1024), (64, 64, 8)]
+    gl = GatheredLinear(sets, device=dev)
+    for step in range(2):
+        gl.begin_step()
+        for i, (bt, h, v) in enumerate(sets):
+            x = torch.randn(bt, h, generator=g).bfloat16().to(DEV)
+            w = (torch.randn(v, h, generator=g) * 0.05).bfloat16().to(DEV)
+            gl.push(i, x)
+            assert torch.equal(gl.gathered_input(i), x)
+            ref = x.double() @ w.double().t()
+            lib = torch.nn.functional.linear(x, w)
+            scale = ref.abs().max().item()
+            err_lib = (lib.double() - ref).abs().max().item()
+            for full in (False, True):
+                y = gl.linear(i, w, full_output=full)
+                assert y.shape == (bt, v)
+                err = (y.double() - ref).abs().max().item()
+                assert err <= 2.0 * err_lib + 1e-3 * scale, (i, full, err, err_lib)
+    torch.cuda.synchronize()
+    assert _lib.read_status(dev) == 0
+    if own_group:
+        dist.destroy_process_group()
