@@ -72,6 +72,9 @@ def main():
     ap.add_argument("--graph", action="store_true",
                     help="capture forward + backward (with the fused updates) + the small optimizer into one CUDA "
                          "graph and replay it; hyper-parameters reach the fused kernels through device memory")
+    ap.add_argument("--fuse-norm", action="store_true",
+                    help="single GPU: fold input_layernorm into q/k/v and post_attention_layernorm into gate/up "
+                         "(FusedRMSNormLinear: the normalised activation is recomputed in backward, not saved)")
     ap.add_argument("--tp", type=int, default=0,
                     help="row-sharded tensor parallelism over this many ranks (launch with torch.distributed.run); "
                          "uses the decoder of examples/tp_model.py instead of the transformers model")
@@ -84,6 +87,7 @@ def main():
     ap.add_argument("--fused-scatter-sets", choices=("all", "gathered"), default="all",
                     help="--fused-scatter: 'gathered' keeps q/k/v and gate/up (replicated input) on library GEMMs + NCCL "
                          "all-reduce; 'all' also forms their input gradient with one GEMM launch per set whose tiles go to every rank")
+    ap.add_argument("--torch-norm", action="store_true", help="--tp: RMSNorm as torch ops instead of the library's kernels")
     ap.add_argument("--no-group", action="store_true", help="one launch per linear instead of one per decoder layer")
     args = ap.parse_args()
     if args.tp:
@@ -109,6 +113,9 @@ def main():
         from forge_b200 import FusedOptimizerManager, autograd
         autograd.use_forge_dgrad = args.forge_dgrad
         fused = swap_linears(model, args.state, args.forge_dgrad)
+        if args.fuse_norm:
+            from forge_b200.rmsnorm_linear import fuse_rmsnorm_linear_pairs
+            fuse_rmsnorm_linear_pairs(model, state_mode=args.state, weight_decay=0.01)
         manager = FusedOptimizerManager(model)
         if not args.no_group:
             manager.group_updates("layer")
@@ -180,7 +187,8 @@ def main():
         "fused_linears": fused, "median_ms_per_step": statistics.median(times), "min_ms": min(times), "max_ms": max(times),
         "steps": args.steps, "peak_hbm_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
         "first_loss": losses[0], "last_loss": losses[-1], "device_status": status,
-        "forge_dgrad": bool(args.forge_dgrad), "cuda_graph": bool(args.graph), "data": "synthetic uniform tokens, random init",
+        "forge_dgrad": bool(args.forge_dgrad), "fuse_norm": bool(args.fuse_norm and not args.baseline),
+        "cuda_graph": bool(args.graph), "data": "synthetic uniform tokens, random init",
     }))
 
 
@@ -204,6 +212,9 @@ def run_tp(args):
     cfg = dict(CONFIGS[args.model])
     if args.layers:
         cfg["layers"] = args.layers
+    if args.torch_norm:
+        from examples import tp_model
+        tp_model.RMSNorm.library_kernels = False
     model = TPDecoder(cfg, state_mode=args.state, device=dev).train()
     if args.fused_scatter and world > 1:
         model.use_fused_scatter(args.seq, replicated_sets=args.fused_scatter_sets == "all")
@@ -294,7 +305,7 @@ def run_tp(args):
             "device_status": int(stats[2].item()), "cuda_graph": bool(graph is not None),
             "grouped_launches": not args.no_group, "forge_dgrad": bool(args.forge_dgrad),
             "fused_scatter": (args.fused_scatter_sets if args.fused_scatter and world > 1 else False),
-            "fused_gather": bool(args.fused_gather and world > 1), "clocks": clocks,
+            "fused_gather": bool(args.fused_gather and world > 1), "library_rmsnorm": not args.torch_norm, "clocks": clocks,
             "timing": "CUDA events per step, median over steps, max over ranks",
             "data": "synthetic uniform tokens (same on every rank), random init"}))
     sys.stdout.flush()

@@ -114,13 +114,37 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
         return (p * (gout / p.shape[0])).to(ctx.dtype), None, None, None
 
 
+class _LibraryRMSNorm(torch.autograd.Function):
+    """RMSNorm through the library's kernels (one launch forward, two backward) instead of a chain of
+    elementwise torch kernels on fp32 copies of the activation."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, eps):
+        from forge_b200.rmsnorm_linear import rmsnorm_forward
+        ctx.save_for_backward(x, gamma)
+        ctx.eps = eps
+        return rmsnorm_forward(x, gamma, eps)
+
+    @staticmethod
+    def backward(ctx, g):
+        from forge_b200.rmsnorm_linear import rmsnorm_backward
+        x, gamma = ctx.saved_tensors
+        dx, dgamma = rmsnorm_backward(x, gamma, g.contiguous(), ctx.eps)
+        return dx, dgamma, None
+
+
 class RMSNorm(nn.Module):
+    library_kernels = True      # False: torch ops everywhere
+
     def __init__(self, dim, eps):
         super().__init__()
         self.weight = nn.Parameter(torch.ones(dim))
         self.eps = eps
 
     def forward(self, x):
+        if (RMSNorm.library_kernels and x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
+                and x.shape[-1] >= 1024 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384):
+            return _LibraryRMSNorm.apply(x, self.weight, self.eps)
         xf = x.float()
         y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)
         return (y * self.weight.float()).to(x.dtype)
