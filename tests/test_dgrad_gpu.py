@@ -177,3 +177,104 @@ def test_gathered_linear_on_one_rank_equals_the_plain_product():
     assert _lib.read_status(dev) == 0
     if own_group:
         dist.destroy_process_group()
+
+
+def _ptr_array(ptrs):
+    import ctypes
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+def test_two_ranks_emulated_on_one_gpu_through_the_c_abi():
+    """Both ranks of the row-sharded forward and backward products, run one after the other on ONE GPU
+    with every "peer" buffer in local memory (each launch only waits for arrivals that earlier launches
+    have already raised): pushes -> gathered products with pushed outputs -> collect, and the backward's
+    GEMM + reduce-scatter, against the unsharded products.  Then a product whose second input block never
+    arrives: the producer's wait runs out, the status word reads 211 and the context stays usable."""
+    import ctypes
+    from forge_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device(DEV, torch.cuda.current_device())
+    stream = torch.cuda.current_stream().cuda_stream
+    status = _lib.status_word(dev).data_ptr()
+    g = torch.Generator().manual_seed(41)
+    R, BT, H, V = 2, 200, 1280, 528
+    blk, vr = H // R, V // R
+    x = torch.randn(BT, H, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(V, H, generator=g) * 0.05).bfloat16().to(DEV)
+    dy = (torch.randn(BT, V, generator=g) * 1e-2).bfloat16().to(DEV)
+    xg = [torch.zeros(BT, H, dtype=torch.bfloat16, device=DEV) for _ in range(R)]      # each rank's gathered input
+    yg = [torch.zeros(BT, V, dtype=torch.bfloat16, device=DEV) for _ in range(R)]      # each rank's gathered output
+    arr = [torch.zeros(2 * R, dtype=torch.int32, device=DEV) for _ in range(R)]         # [0:R] input, [R:2R] output arrivals
+    counters = torch.zeros(2 * R, dtype=torch.int32, device=DEV)
+    epoch = torch.full((1,), 5, dtype=torch.int32, device=DEV)
+    x_dst, y_dst = _ptr_array([t.data_ptr() for t in xg]), _ptr_array([t.data_ptr() for t in yg])
+    x_arr = _ptr_array([t.data_ptr() for t in arr])
+    y_arr = _ptr_array([t.data_ptr() + 4 * R for t in arr])
+    for r in range(R):
+        xb = x[:, r * blk:(r + 1) * blk]
+        _lib.check(lib.forge_push_block(xb.data_ptr(), BT, blk, xb.stride(0), x_dst, r * blk, H, x_arr,
+                                        counters.data_ptr() + 4 * r, epoch.data_ptr(), r, R, status, stream), "push")
+    for r in range(R):
+        assert torch.equal(xg[r], x)
+    for r in range(R):
+        wr = w[r * vr:(r + 1) * vr]
+        a = _lib.ForgeLinearGatheredArgs()
+        a.X, a.W, a.BT, a.H, a.V_r, a.ld_x, a.ld_w = xg[r].data_ptr(), wr.data_ptr(), BT, H, vr, H, wr.stride(0)
+        a.x_arrivals, a.epoch, a.rank, a.world = arr[r].data_ptr(), epoch.data_ptr(), r, R
+        a.y, a.y_dst, a.y_col, a.y_pitch, a.y_arrivals = None, y_dst, r * vr, V, y_arr
+        a.y_counter, a.status = counters.data_ptr() + 4 * (R + r), status
+        _lib.check(lib.forge_linear_gathered(ctypes.byref(a), stream), "forge_linear_gathered")
+    ref = x.double() @ w.double().t()
+    lib_y = torch.nn.functional.linear(x, w)
+    err_lib = (lib_y.double() - ref).abs().max().item()
+    outs = []
+    for r in range(R):
+        out = torch.empty(BT, V, dtype=torch.bfloat16, device=DEV)
+        _lib.check(lib.forge_collect(yg[r].data_ptr(), V, arr[r].data_ptr() + 4 * R, epoch.data_ptr(), out.data_ptr(), BT, V, V,
+                                     R, status, stream), "forge_collect")
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    assert (outs[0].double() - ref).abs().max().item() <= 2.0 * err_lib + 1e-3 * ref.abs().max().item()
+    # backward: every rank's partial dX tiles into the owners' slots, then each owner's sum
+    slots = [torch.zeros(R, BT, blk, dtype=torch.bfloat16, device=DEV) for _ in range(R)]
+    sarr = [torch.zeros(R, dtype=torch.int32, device=DEV) for _ in range(R)]
+    sc = torch.zeros(R, dtype=torch.int32, device=DEV)
+    s_ptrs, a_ptrs = _ptr_array([t.data_ptr() for t in slots]), _ptr_array([t.data_ptr() for t in sarr])
+    for r in range(R):
+        dyr, wr = dy[:, r * vr:(r + 1) * vr].contiguous(), w[r * vr:(r + 1) * vr]
+        seg = (_lib.ForgeDgradSegment * 1)()
+        seg[0].dY, seg[0].W, seg[0].V, seg[0].ld_dy, seg[0].ld_w = dyr.data_ptr(), wr.data_ptr(), vr, dyr.stride(0), wr.stride(0)
+        a = _lib.ForgeDgradScatterArgs()
+        a.segments, a.count, a.BT, a.H, a.slots, a.arrivals = seg, 1, BT, H, s_ptrs, a_ptrs
+        a.counter, a.epoch, a.rank, a.world, a.status, a.all_ranks = sc.data_ptr() + 4 * r, epoch.data_ptr(), r, R, status, 0
+        _lib.check(lib.forge_dgrad_scatter(ctypes.byref(a), stream), "forge_dgrad_scatter")
+        torch.cuda.synchronize()          # dyr stays alive until its launch has run
+    ref_dx = dy.double() @ w.double()
+    lib_dx = dy @ w
+    err_lib = (lib_dx.double() - ref_dx).abs().max().item()
+    for r in range(R):
+        out = torch.empty(BT, blk, dtype=torch.bfloat16, device=DEV)
+        _lib.check(lib.forge_reduce_slots(slots[r].data_ptr(), sarr[r].data_ptr(), epoch.data_ptr(), out.data_ptr(), BT, blk, blk,
+                                          R, status, stream), "forge_reduce_slots")
+        err = (out.double() - ref_dx[:, r * blk:(r + 1) * blk]).abs().max().item()
+        assert err <= 3.0 * err_lib + 1e-3 * ref_dx.abs().max().item(), (r, err, err_lib)
+    torch.cuda.synchronize()
+    assert _lib.read_status(dev) == 0
+    # a block that never arrives
+    epoch.add_(1)
+    out = torch.full((BT, vr), 3.0, dtype=torch.bfloat16, device=DEV)
+    wr = w[:vr]
+    a = _lib.ForgeLinearGatheredArgs()
+    a.X, a.W, a.BT, a.H, a.V_r, a.ld_x, a.ld_w = xg[0].data_ptr(), wr.data_ptr(), BT, H, vr, H, wr.stride(0)
+    a.x_arrivals, a.epoch, a.rank, a.world = arr[0].data_ptr(), epoch.data_ptr(), 0, R
+    a.y, a.ld_y, a.status = out.data_ptr(), vr, status
+    assert lib.forge_set_arrival_wait_ns(20_000_000) == 0
+    _lib.check(lib.forge_linear_gathered(ctypes.byref(a), stream), "forge_linear_gathered")
+    torch.cuda.synchronize()
+    assert lib.forge_set_arrival_wait_ns(2_000_000_000) == 0
+    with pytest.raises(_lib.ForgeLibraryError, match="211"):
+        _lib.read_status(dev)
+    # the context is still usable
+    assert torch.equal(K.dgrad(dy, w).view(torch.int16), K.dgrad(dy, w).view(torch.int16))
+    torch.cuda.synchronize()
+    assert _lib.read_status(dev) == 0
