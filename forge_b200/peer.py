@@ -27,10 +27,17 @@ import torch.distributed as dist
 from forge_b200 import _lib
 
 
+def _world_and_rank(group=None):
+    """(1, 0) in a process without a process group: the single-GPU forms of the kernels."""
+    if not dist.is_initialized():
+        return 1, 0
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
 def _share(t: torch.Tensor, group=None) -> list[torch.Tensor]:
     """Views of every rank's tensor `t` (same shape everywhere) mapped into this process."""
     from torch.multiprocessing.reductions import reduce_tensor
-    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    world, rank = _world_and_rank(group)
     if world == 1:
         return [t]
     fn, args = reduce_tensor(t)
@@ -63,7 +70,7 @@ class DgradReduceScatter:
 
     def __init__(self, sets, group=None, device=None):
         self.group = group
-        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.world, self.rank = _world_and_rank(group)
         if self.world > 8:
             raise ValueError("at most 8 ranks")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -163,7 +170,7 @@ class GatheredLinear:
 
     def __init__(self, sets, group=None, device=None):
         self.group = group
-        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.world, self.rank = _world_and_rank(group)
         if self.world > 8:
             raise ValueError("at most 8 ranks")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

@@ -142,17 +142,8 @@ def test_scatter_and_reduce_on_one_rank_equal_the_plain_gemm():
 def test_gathered_linear_on_one_rank_equals_the_plain_product():
     """The forward GEMM of the row-sharded mode with a world of one: push of the (only) input block, the
     K-major product, both output forms (local TMA store; peer-store epilogue + collect), ragged sizes."""
-    import torch.distributed as dist
     from forge_b200 import _lib
     from forge_b200.peer import GatheredLinear
-    own_group = not dist.is_initialized()
-    if own_group:
-        import socket
-        sock = socket.socket()
-        sock.bind(("127.0.0.1", 0))
-        port = sock.getsockname()[1]
-        sock.close()
-        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
     g = torch.Generator().manual_seed(31)
     dev = torch.device(DEV, torch.cuda.current_device())
     sets = [(200, 1000, 264), (512, 4096, 1024), (64, 64, 8)]
@@ -175,8 +166,6 @@ def test_gathered_linear_on_one_rank_equals_the_plain_product():
                 assert err <= 2.0 * err_lib + 1e-3 * scale, (i, full, err, err_lib)
     torch.cuda.synchronize()
     assert _lib.read_status(dev) == 0
-    if own_group:
-        dist.destroy_process_group()
 
 
 def _ptr_array(ptrs):

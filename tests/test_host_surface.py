@@ -248,3 +248,14 @@ def test_layer_groups_are_formed_by_name_prefix():
     mixed.layers[0].attn["k"] = FusedLinear(64, 16, state_mode="int8")
     g = FusedOptimizerManager(mixed).group_updates("layer")._update_groups
     assert sorted(len(x) for x in g) == [6, 7]          # the int8 module cannot share a launch with bf16 ones
+
+
+def test_peer_helpers_work_without_a_process_group():
+    """A single-GPU process never initialises torch.distributed: the peer-memory classes then run their
+    one-rank forms."""
+    import torch.distributed as dist
+    from forge_b200 import peer
+    if not dist.is_initialized():
+        assert peer._world_and_rank() == (1, 0)
+        t = torch.zeros(4)
+        assert peer._share(t)[0] is t
