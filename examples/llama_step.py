@@ -105,6 +105,7 @@ def main():
     model.train()
     model.config.use_cache = False
     n_params = sum(p.numel() for p in model.parameters())
+    mem = {"parameters_gb": torch.cuda.memory_allocated(dev) / 1e9}
 
     if args.baseline:
         opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01, fused=True, capturable=args.graph)
@@ -175,6 +176,9 @@ def main():
         if step >= args.warmup:
             times.append((time.perf_counter() - t0) * 1e3)
         losses.append(loss.item())
+        if step == 0:      # parameters + every optimizer state, nothing of the step itself
+            del loss
+            mem["parameters_and_state_gb"] = torch.cuda.memory_allocated(dev) / 1e9
     clocks = sampler.stop()
     status = 0
     if manager is not None:
@@ -185,7 +189,7 @@ def main():
         "model": args.model, "layers": cfg.num_hidden_layers, "parameters": n_params, "seq": args.seq, "batch": 1,
         "impl": "torch AdamW(fused=True) baseline" if args.baseline else f"forge_b200 fused linears ({args.state} moments)",
         "fused_linears": fused, "median_ms_per_step": statistics.median(times), "min_ms": min(times), "max_ms": max(times),
-        "steps": args.steps, "peak_hbm_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
+        "steps": args.steps, "peak_hbm_gb": torch.cuda.max_memory_allocated(dev) / 1e9, "memory": mem,
         "first_loss": losses[0], "last_loss": losses[-1], "device_status": status,
         "forge_dgrad": bool(args.forge_dgrad), "fuse_norm": bool(args.fuse_norm and not args.baseline),
         "cuda_graph": bool(args.graph), "data": "synthetic uniform tokens, random init",
