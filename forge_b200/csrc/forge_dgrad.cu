@@ -31,6 +31,7 @@
 //     transfer of those that are not.  With the peer-store epilogue the output tiles go to every rank's
 //     gathered Y (the all-gather of the row-sharded output), otherwise to local memory by TMA.
 #include <cuda_bf16.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -43,14 +44,18 @@ namespace forge {
 
 namespace dg {
 constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int STAGES = 6;
+constexpr int STAGES = 6;                       // single CTAs
+constexpr int STAGES_PAIR = 7;                  // CTA pairs: each CTA stages its A rows and HALF of the B tile
 constexpr int A_BYTES = BM * BK * 2;            // 16 KB, K-major, 128-byte swizzle
 constexpr int B_BYTES = BK * BN * 2;            // 16 KB, two N-major slabs of 64 columns
 constexpr int B_SLAB = 64 * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int OUT_BYTES = BM * BN * 2;          // staging tile, two boxes of 64 columns
 constexpr int CTRL_BYTES = 1024;
+constexpr int STAGE_BYTES_PAIR = A_BYTES + B_BYTES / 2;
 constexpr int SMEM_BYTES = CTRL_BYTES + 1024 + STAGES * STAGE_BYTES + OUT_BYTES;
+constexpr int SMEM_BYTES_PAIR = CTRL_BYTES + 1024 + STAGES_PAIR * STAGE_BYTES_PAIR + OUT_BYTES;
+constexpr int MAX_STAGES = STAGES_PAIR;
 constexpr int THREADS = 256;
 constexpr int ACC_BUFS = 4;
 constexpr int TMEM_COLS = 512;
@@ -60,8 +65,8 @@ constexpr int MAX_RANKS = 8;
 enum : int { ERR_OP_EMPTY = 201, ERR_OP_FULL = 202, ERR_ACC_EMPTY = 203, ERR_ACC_FULL = 204, ERR_ARRIVAL = 211 };
 
 struct Ctrl {
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t acc_full[ACC_BUFS];
   uint64_t acc_empty[ACC_BUFS];
   uint32_t tmem_base;
@@ -87,6 +92,7 @@ struct Params {
   int push_pitch, push_col;
   const uint32_t* seg_arrival[MAX_SEG];        // FWD: local arrival word of the block behind segment i, or NULL
   unsigned long long wait_ns;                  // FWD: how long the producer waits for a block
+  int prefetch_kb;                             // the producer asks the L2 for B's tiles this many K blocks ahead
   uint8_t* slots[MAX_RANKS];                   // receive buffer of every rank, (world, M, block_cols) bf16
   uint32_t* arrivals[MAX_RANKS];               // arrival words of every rank, `world` each; [rank] is written here
   uint32_t* counter;                           // local: CTAs of this launch that have finished
@@ -95,27 +101,42 @@ struct Params {
 };
 }  // namespace dg
 
-template <bool SCATTER, bool FWD>
+// CG = 2: a pair of CTAs (cluster of two, tcgen05 cta_group::2) shares a 256 x 128 tile.  Each CTA stages
+// its own 128 rows of A and 64 of the tile's 128 columns of B (the MMA reads the two halves from the
+// two CTAs' shared memory), so a stage is 24 KB instead of 32 KB for the same MMA work per SM.  The
+// leader (rank 0) issues the MMAs; both CTAs' copies count on the leader's full barrier; its commits
+// arrive on both CTAs' barriers (a barrier signal, not a data copy).
+template <bool SCATTER, bool FWD, int CG>
 __global__ void __launch_bounds__(dg::THREADS, 1)
 forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ dg::Params p) {
   using namespace dg;
+  constexpr int NSTAGE = CG == 2 ? STAGES_PAIR : STAGES;
+  constexpr int STAGE_B = CG == 2 ? STAGE_BYTES_PAIR : STAGE_BYTES;
+  const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const int first_tile = (CG == 2) ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
+  const int tile_step = static_cast<int>(gridDim.x) / CG;
   extern __shared__ uint8_t smem_raw[];
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw);
   uint8_t* data = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + CTRL_BYTES + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* out_buf = data + STAGES * STAGE_BYTES;
+  uint8_t* out_buf = data + NSTAGE * STAGE_B;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_word = &ctrl->abort_word;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < STAGES; ++i) { mbar_init(&ctrl->full[i], 1); mbar_init(&ctrl->empty[i], 1); }
-    for (int i = 0; i < ACC_BUFS; ++i) { mbar_init(&ctrl->acc_full[i], 1); mbar_init(&ctrl->acc_empty[i], 4); }
+    for (int i = 0; i < NSTAGE; ++i) { mbar_init(&ctrl->full[i], 1); mbar_init(&ctrl->empty[i], 1); }
+    for (int i = 0; i < ACC_BUFS; ++i) { mbar_init(&ctrl->acc_full[i], 1); mbar_init(&ctrl->acc_empty[i], 4 * CG); }
     ctrl->abort_word = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(&ctrl->tmem_base, TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (CG == 2) {
+      tmem_alloc_pair(&ctrl->tmem_base, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&ctrl->tmem_base, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   if (warp == 0 && lane == 0) {
     prefetch_tmap(&p.seg[0].tm_a);
@@ -124,8 +145,10 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();   // the peer's barriers exist before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
+  // p.tiles_m counts tiles of BM * CG rows
   const int num_tiles = p.tiles_m * p.tiles_n;
 
   if (warp == 0) {
@@ -134,9 +157,9 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
       const uint64_t pol_b = policy_evict_first();   // W streams through once per row of tiles
       uint32_t it = 0;
       uint32_t arrived = 0;                          // FWD: segments whose block is known to be here
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      for (int tile = first_tile; tile < num_tiles; tile += tile_step) {
         // consecutive CTAs share a column panel of W: tile index runs over M fastest
-        const int m0 = (tile % p.tiles_m) * BM;
+        const int m0 = (tile % p.tiles_m) * (BM * CG) + static_cast<int>(cta_rank) * BM;
         const int n0 = (tile / p.tiles_m) * BN;
         for (int sg = 0; sg < p.nseg; ++sg) {
           const CUtensorMap* tm_a = &p.seg[sg].tm_a;
@@ -161,41 +184,72 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
               arrived |= 1u << sg;
             }
           }
-          for (int kb = 0; kb < nkb; ++kb, ++it) {
-            const int s = it % STAGES;
-            const uint32_t ph = (it / STAGES) & 1;
-            if (!mbar_wait(&ctrl->empty[s], ph ^ 1, abort_word, ERR_OP_EMPTY)) goto done;
-            uint8_t* a = data + s * STAGE_BYTES;
-            uint8_t* b = a + A_BYTES;
-            mbar_expect_tx(&ctrl->full[s], STAGE_BYTES);
-            // rows / columns past the end of a segment are zero-filled and add nothing
-            tma_load_2d(a, tm_a, &ctrl->full[s], kb * BK, m0, pol_a);
+          // W streams from HBM once and its latency is what the ring cannot cover: request its tiles a few
+          // K blocks before the loads that need them (one request per 64 x 64-element box)
+          auto prefetch_b = [&](int kb) {
             if constexpr (FWD) {
-              tma_load_2d(b, tm_b, &ctrl->full[s], kb * BK, n0, pol_b);          // 128 rows of W_r, K-major
+              if constexpr (CG == 2) {
+                tma_prefetch_2d(tm_b, kb * BK, n0 + static_cast<int>(cta_rank) * 64);
+              } else {
+                tma_prefetch_2d(tm_b, kb * BK, n0);
+              }
             } else {
-              tma_load_2d(b, tm_b, &ctrl->full[s], n0, kb * BK, pol_b);
-              tma_load_2d(b + B_SLAB, tm_b, &ctrl->full[s], n0 + 64, kb * BK, pol_b);
+              if constexpr (CG == 2) {
+                tma_prefetch_2d(tm_b, n0 + static_cast<int>(cta_rank) * 64, kb * BK);
+              } else {
+                tma_prefetch_2d(tm_b, n0, kb * BK);
+                tma_prefetch_2d(tm_b, n0 + 64, kb * BK);
+              }
+            }
+          };
+          const int pf = p.prefetch_kb;
+          for (int kb = 0; kb < pf && kb < nkb; ++kb) prefetch_b(kb);
+          for (int kb = 0; kb < nkb; ++kb, ++it) {
+            const int s = it % NSTAGE;
+            const uint32_t ph = (it / NSTAGE) & 1;
+            if (pf > 0 && kb + pf < nkb) prefetch_b(kb + pf);
+            if (!mbar_wait(&ctrl->empty[s], ph ^ 1, abort_word, ERR_OP_EMPTY)) goto done;
+            uint8_t* a = data + s * STAGE_B;
+            uint8_t* b = a + A_BYTES;
+            // rows / columns past the end of a segment are zero-filled and add nothing
+            if constexpr (CG == 2) {
+              // both CTAs' copies count on the LEADER's barrier; the leader expects the bytes of both
+              const uint32_t full_leader = map_to_cta(smem_u32(&ctrl->full[s]), 0);
+              if (cta_rank == 0) mbar_expect_tx(&ctrl->full[s], 2 * STAGE_BYTES_PAIR);
+              const int nh = n0 + static_cast<int>(cta_rank) * 64;        // this CTA's half of the tile's columns
+              tma_load_2d_pair(a, tm_a, full_leader, kb * BK, m0, pol_a);
+              if constexpr (FWD) tma_load_2d_pair(b, tm_b, full_leader, kb * BK, nh, pol_b);   // 64 rows of W_r, K-major
+              else tma_load_2d_pair(b, tm_b, full_leader, nh, kb * BK, pol_b);
+            } else {
+              mbar_expect_tx(&ctrl->full[s], STAGE_BYTES);
+              tma_load_2d(a, tm_a, &ctrl->full[s], kb * BK, m0, pol_a);
+              if constexpr (FWD) {
+                tma_load_2d(b, tm_b, &ctrl->full[s], kb * BK, n0, pol_b);          // 128 rows of W_r, K-major
+              } else {
+                tma_load_2d(b, tm_b, &ctrl->full[s], n0, kb * BK, pol_b);
+                tma_load_2d(b + B_SLAB, tm_b, &ctrl->full[s], n0 + 64, kb * BK, pol_b);
+              }
             }
           }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, false, !FWD);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM * CG, BN, false, !FWD);
       uint32_t it = 0, tile_it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_it) {
+      for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++tile_it) {
         const int buf = tile_it % ACC_BUFS;
         const uint32_t aph = (tile_it / ACC_BUFS) & 1;
         if (!mbar_wait(&ctrl->acc_empty[buf], aph ^ 1, abort_word, ERR_ACC_EMPTY)) goto done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < p.total_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+          const int s = it % NSTAGE;
+          const uint32_t ph = (it / NSTAGE) & 1;
           if (!mbar_wait(&ctrl->full[s], ph, abort_word, ERR_OP_FULL)) goto done;
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(data + s * STAGE_BYTES);
+          const uint32_t a_addr = smem_u32(data + s * STAGE_B);
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
@@ -206,11 +260,15 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
             // FWD: B is K-major like A (128 rows of W_r, 8-row groups 1024 bytes apart)
             const uint64_t db = FWD ? make_smem_desc_sw128(b_addr + k * 32, 16, 1024)
                                     : make_smem_desc_sw128(b_addr + k * 2048, B_SLAB, 1024);
-            umma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if constexpr (CG == 2) umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else umma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&ctrl->empty[s]);
+          // frees the stage in both CTAs of a pair
+          if constexpr (CG == 2) umma_commit_pair(&ctrl->empty[s], 3);
+          else umma_commit(&ctrl->empty[s]);
         }
-        umma_commit(&ctrl->acc_full[buf]);
+        if constexpr (CG == 2) umma_commit_pair(&ctrl->acc_full[buf], 3);
+        else umma_commit(&ctrl->acc_full[buf]);
       }
     }
   } else if (warp >= 4) {
@@ -218,8 +276,8 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
     const int r = quarter * 32 + lane;
     const uint64_t pol = policy_evict_last();   // dX is consumed by the next backward kernel
     uint32_t tile_it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_it) {
-      const int m0 = (tile % p.tiles_m) * BM;
+    for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++tile_it) {
+      const int m0 = (tile % p.tiles_m) * (BM * CG) + static_cast<int>(cta_rank) * BM;
       const int n0 = (tile / p.tiles_m) * BN;
       const int buf = tile_it % ACC_BUFS;
       const uint32_t aph = (tile_it / ACC_BUFS) & 1;
@@ -260,7 +318,8 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(&ctrl->acc_empty[buf]);
+          if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&ctrl->acc_empty[buf]), 0));
+          else mbar_arrive(&ctrl->acc_empty[buf]);
           const int rr = m0 + quarter * 32;
           if (rr < p.M) {
             if (n0 < p.N) tma_store_2d(&tm_out, out_buf + quarter * 32 * 128, n0, rr, pol);
@@ -271,7 +330,10 @@ forge_dgrad_kernel(const __grid_constant__ CUtensorMap tm_out, const __grid_cons
         __syncwarp();
       } else {
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ctrl->acc_empty[buf]);
+        if (lane == 0) {
+          if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&ctrl->acc_empty[buf]), 0));
+          else mbar_arrive(&ctrl->acc_empty[buf]);
+        }
         // This warp's 32 rows of the staging tile go to the owner of the tile's feature block: slot
         // [this rank] of its receive buffer, row m, column n - owner * block_cols.  Two rows per
         // instruction, sixteen lanes x 16 bytes = one 256-byte run per row.
@@ -329,9 +391,12 @@ done:
       }
     }
   }
+  // a pair leaves together: the peer's shared memory and barriers stay valid until both are done
+  if constexpr (CG == 2) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -413,9 +478,23 @@ int launch_dgrad(const ForgeDgradSegment* segs, int nseg, void* dX, int64_t BT, 
     if (dX == nullptr) return fail(FORGE_ERR_INVALID_ARG, "dX is NULL");
     if ((rc = encode_tmap_2d(&tm_out, dX, 2, true, BT, H, ld_dx, 64, 32, 128)) != FORGE_OK) return rc;
   }
+  // CTA pairs (FORGE_DGRAD_PAIRS=1) when there is more than one 128-row tile to pair up.  Off by default:
+  // measured at BT = 512 they run at the rate of single CTAs (both forms are bound by the depth of the
+  // operand ring against the latency of the W stream, not by the bytes a stage moves).
+  static const bool pairs_allowed = [] {
+    const char* e = getenv("FORGE_DGRAD_PAIRS");
+    return e != nullptr && e[0] == '1';
+  }();
+  const int cg = (pairs_allowed && BT > BM) ? 2 : 1;
+  static const int prefetch_kb = [] {
+    const char* e = getenv("FORGE_DGRAD_PREFETCH");
+    const int v = e != nullptr ? atoi(e) : 0;     // measured: no gain at 8 / 16 / 32 blocks ahead
+    return v < 0 ? 0 : (v > 64 ? 64 : v);
+  }();
+  p.prefetch_kb = prefetch_kb;
   p.M = static_cast<int>(BT);
   p.N = static_cast<int>(H);
-  p.tiles_m = static_cast<int>((BT + BM - 1) / BM);
+  p.tiles_m = static_cast<int>((BT + BM * cg - 1) / (BM * cg));
   p.tiles_n = static_cast<int>((H + BN - 1) / BN);
   p.nseg = 0;
   p.total_kb = 0;
@@ -428,8 +507,8 @@ int launch_dgrad(const ForgeDgradSegment* segs, int nseg, void* dX, int64_t BT, 
     p.seg_arrival[p.nseg] = p.seg_arrival[i];      // (FWD) follows its segment when empty ones are dropped
     Segment& sg = p.seg[p.nseg++];
     if ((rc = encode_tmap_2d(&sg.tm_a, g.dY, 2, true, BT, g.V, g.ld_dy, BK, BM, 128)) != FORGE_OK) return rc;
-    if (FWD) {   // W_r block: H rows (the output columns) of g.V contiguous K elements
-      if ((rc = encode_tmap_2d(&sg.tm_b, g.W, 2, true, H, g.V, g.ld_w, BK, BN, 128)) != FORGE_OK) return rc;
+    if (FWD) {   // W_r block: H rows (the output columns) of g.V contiguous K elements; a pair's CTA takes 64 rows
+      if ((rc = encode_tmap_2d(&sg.tm_b, g.W, 2, true, H, g.V, g.ld_w, BK, BN / cg, 128)) != FORGE_OK) return rc;
     } else {
       if ((rc = encode_tmap_2d(&sg.tm_b, g.W, 2, true, g.V, H, g.ld_w, 64, BK, 128)) != FORGE_OK) return rc;
     }
@@ -441,19 +520,38 @@ int launch_dgrad(const ForgeDgradSegment* segs, int nseg, void* dX, int64_t BT, 
     p.seg[0].tm_b = tm_out;
     p.seg[0].num_kb = 0;
   }
-  auto kern = forge_dgrad_kernel<SCATTER, FWD>;
-  static std::atomic<bool> attr_set[64];   // per device: the shared-memory opt-in has been made
+  static std::atomic<bool> attr_set[64][2];   // per device and form: the shared-memory opt-in has been made
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  const int smem = cg == 2 ? SMEM_BYTES_PAIR : SMEM_BYTES;
+  if (dev >= 0 && dev < 64 && !attr_set[dev][cg - 1].load(std::memory_order_acquire)) {
+    cudaError_t e = cg == 2 ? cudaFuncSetAttribute(forge_dgrad_kernel<SCATTER, FWD, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+                            : cudaFuncSetAttribute(forge_dgrad_kernel<SCATTER, FWD, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set[dev].store(true, std::memory_order_release);
+    attr_set[dev][cg - 1].store(true, std::memory_order_release);
   }
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
-  const int grid = static_cast<int>(std::min<int64_t>(tiles, di->sm_count));
-  kern<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_out, p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e;
+  if (cg == 2) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * static_cast<unsigned>(std::min<int64_t>(tiles, di->sm_count / 2)), 1, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, forge_dgrad_kernel<SCATTER, FWD, 2>, tm_out, p);
+  } else {
+    const int grid = static_cast<int>(std::min<int64_t>(tiles, di->sm_count));
+    forge_dgrad_kernel<SCATTER, FWD, 1><<<grid, THREADS, smem, stream>>>(tm_out, p);
+    e = cudaGetLastError();
+  }
   if (e != cudaSuccess) return fail(FORGE_ERR_CUDA, "dgrad kernel launch: %s", cudaGetErrorString(e));
   return FORGE_OK;
 }

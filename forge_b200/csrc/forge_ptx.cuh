@@ -102,6 +102,13 @@ __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
 
+// ask the L2 for a tile ahead of the load that will want it (no shared memory, no barrier)
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y)
+               : "memory");
+}
+
 __device__ __forceinline__ void prefetch_l2(const void* gptr) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(gptr) : "memory");
 }
