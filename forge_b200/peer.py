@@ -90,6 +90,7 @@ class DgradReduceScatter:
             offs.append(total)
             total += (bt * h * 2 * (self.world if everywhere else 1) + 255) // 256 * 256
         self._slot_off = offs
+        self._used: set[int] = set()
         n = len(self.sets)
         self.slots = torch.zeros(max(total, 256), dtype=torch.uint8, device=self.device)
         self.arrivals = torch.zeros(max(n * self.world, 1), dtype=torch.int32, device=self.device)
@@ -108,11 +109,16 @@ class DgradReduceScatter:
 
     def begin_step(self):
         self.epoch.add_(1)
+        self._used.clear()
 
     def run(self, index: int, members, out: torch.Tensor | None = None, reduce_stream=None) -> torch.Tensor:
         """``reduce_stream``: run the owner's wait-and-sum there (after the GEMM, by an event) so that the
         current stream can go on while the peers' tiles are still arriving; the caller orders its use of
         the result after that stream."""
+        if index in self._used:
+            # a second launch would store into receive buffers that a peer may still be summing
+            raise RuntimeError(f"set {index} has already run in this step; call begin_step() between steps")
+        self._used.add(index)
         bt, h = self.sets[index]
         everywhere = self.all_ranks[index]
         s = h if everywhere else h // self.world
@@ -185,6 +191,7 @@ class GatheredLinear:
             total_x += (bt * h * 2 + 255) // 256 * 256
             total_y += (bt * v * 2 + 255) // 256 * 256
         self._x_off, self._y_off = xo, yo
+        self._pushed: set[int] = set()
         n = len(self.sets)
         self.x_buf = torch.zeros(max(total_x, 256), dtype=torch.uint8, device=self.device)
         self.y_buf = torch.zeros(max(total_y, 256), dtype=torch.uint8, device=self.device)
@@ -207,6 +214,7 @@ class GatheredLinear:
 
     def begin_step(self):
         self.epoch.add_(1)
+        self._pushed.clear()
         if self.world > 1:
             dist.all_reduce(self.tick, group=self.group)
 
@@ -220,6 +228,10 @@ class GatheredLinear:
         blk = h // self.world
         if x_block.dtype != torch.bfloat16 or tuple(x_block.shape) != (bt, blk) or x_block.stride(1) != 1:
             raise ValueError(f"expected a bf16 ({bt}, {blk}) block with contiguous rows")
+        if index in self._pushed:
+            # the gathered input of the first pass is still wanted by its backward pass (and by peers' products)
+            raise RuntimeError(f"set {index} has already been pushed in this step; call begin_step() between steps")
+        self._pushed.add(index)
         lib = _lib.load()
         with torch.cuda.device(self.device):
             _lib.check(lib.forge_push_block(x_block.data_ptr(), bt, blk, x_block.stride(0), self._x_dst[index],

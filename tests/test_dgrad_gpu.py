@@ -116,6 +116,8 @@ def test_scatter_and_reduce_on_one_rank_equal_the_plain_gemm():
         out = rs.run(2, ragged)
         assert out.shape == (BT, 1000)
         assert torch.equal(out.view(torch.int16), K.dgrad_sum(ragged).view(torch.int16))
+    with pytest.raises(RuntimeError, match="already run"):
+        rs.run(1, small)                          # twice in one step: the receive buffers are still in use
     torch.cuda.synchronize()
     dev = torch.device(DEV, torch.cuda.current_device())
     assert _lib.read_status(dev) == 0
@@ -164,6 +166,8 @@ def test_gathered_linear_on_one_rank_equals_the_plain_product():
                 assert y.shape == (bt, v)
                 err = (y.double() - ref).abs().max().item()
                 assert err <= 2.0 * err_lib + 1e-3 * scale, (i, full, err, err_lib)
+    with pytest.raises(RuntimeError, match="already been pushed"):
+        gl.push(0, torch.zeros(200, 1000, dtype=torch.bfloat16, device=DEV))      # a second forward in one step
     torch.cuda.synchronize()
     assert _lib.read_status(dev) == 0
 
