@@ -71,6 +71,23 @@ def _worker(rank, world, port, result):
         assert torch.allclose(lin.weight.grad, full_dw[r0:r1], atol=1e-4)
         assert torch.equal(lin.gather_full_weight(), w)
         assert torch.equal(gather_rows(w[r0:r1], V, rank, world), w)
+        # a set of linears on one replicated input: on the host (no fused collective attached, CPU tensors)
+        # it runs its members one by one and says that the input gradient still has to be summed
+        from forge_b200.tensor_parallel import RowShardedLinearSet
+        members = [RowShardedFusedLinear.from_full_weight(w, gather_input=False),
+                   RowShardedFusedLinear.from_full_weight(w[:16], gather_input=False)]
+        group = RowShardedLinearSet(members)
+        assert not list(group.parameters()), "the set does not own its members"
+        xr = x.clone().requires_grad_(True)
+        assert not group.fused(xr)
+        outs, complete = group(xr)
+        assert not complete and len(outs) == 2
+        assert torch.allclose(outs[0], full_y[..., members[0].row_start:members[0].row_end], atol=1e-5)
+        with pytest.raises(ValueError):
+            RowShardedLinearSet([lin])                       # gathers its own input: not a member of a set
+        with pytest.raises(ValueError):
+            RowShardedLinearSet([members[0], RowShardedFusedLinear(8, 16, gather_input=False)])   # another input
+        assert not lin.returns_full_output(xs)
         result.put((rank, "ok"))
     except Exception as e:  # pragma: no cover
         result.put((rank, f"{type(e).__name__}: {e}"))
