@@ -303,7 +303,12 @@ def run_tp(args):
         print(json.dumps({
             "model": args.model, "layers": cfg["layers"], "parameters": n_total, "parameters_per_rank": n_local,
             "seq": args.seq, "batch": 1, "tp": world,
-            "impl": f"forge_b200 row-sharded fused linears ({args.state} moments), NCCL all-gather / reduce-scatter",
+            "impl": f"forge_b200 row-sharded fused linears ({args.state} moments), " + (
+                "NCCL all-gather / reduce-scatter" if not (args.fused_gather or args.fused_scatter) or world == 1 else
+                "collectives of o / down" + (" and of q/k/v, gate/up" if args.fused_scatter and args.fused_scatter_sets == "all" else "")
+                + " fused into this library's GEMMs (" + " + ".join(
+                    n for n, on in (("forward gathers", args.fused_gather), ("backward scatters", args.fused_scatter)) if on)
+                + "), NCCL for the rest"),
             "median_ms_per_step": ms, "tokens_per_s": args.seq / (ms * 1e-3), "steps": args.steps,
             "peak_hbm_gb_per_rank": stats[1].item(), "first_loss": losses[0], "last_loss": losses[-1],
             "device_status": int(stats[2].item()), "cuda_graph": bool(graph is not None),
