@@ -653,7 +653,7 @@ def run_forge(args):
 
     # the sharded mode's full linear backward (see step_tp), and what each part costs alone
     tp_steps = max(1, min(args.steps, 5))
-    tp_ms = {}
+    tp_ms, tp_errors = {}, {}
     if not args.no_tp_step:
         variants = [("step", dict()), ("dx_gemm", dict(parts=("dx",))), ("update", dict(parts=("update",)))]
         if world > 1:
@@ -664,15 +664,25 @@ def run_forge(args):
             variants.append(("step_fused", None))
         for label, kw in variants:
             fn = step_tp_fused if kw is None else (lambda kw: (lambda step_no=None: step_tp(step_no, **kw)))(kw)
-            set_step(step_no)
-            fn()
-            g_tp = capture(fn)
-            set_step(step_no)
-            g_tp.replay() if g_tp is not None else fn()
-            tp_ms[label], _ = timed(fn, tp_steps, step_no, graph=g_tp)
-            del g_tp
+            # these records explain the mode around the path; none of them may cost the headline its line
+            try:
+                set_step(step_no)
+                fn()
+                g_tp = capture(fn)
+                set_step(step_no)
+                g_tp.replay() if g_tp is not None else fn()
+                tp_ms[label], _ = timed(fn, tp_steps, step_no, graph=g_tp)
+                del g_tp
+            except Exception as e:  # noqa: BLE001
+                tp_ms[label] = None
+                tp_errors[label] = f"{type(e).__name__}: {e}"[:300]
         step_no += 1
-    parity = tp_parity_check() if world > 1 else None
+    parity = None
+    if world > 1:
+        try:
+            parity = tp_parity_check()
+        except Exception as e:  # noqa: BLE001
+            tp_errors["tp_parity"] = f"{type(e).__name__}: {e}"[:300]
     status = _lib.read_status(dev)
 
     peak_gb = torch.cuda.max_memory_allocated(dev) / 1e9
@@ -719,7 +729,7 @@ def run_forge(args):
             line["tp_step"] = {
                 "what": "per set of linears sharing an input: partial dX GEMM and NCCL reduce-scatter of dX on a communication "
                         "stream; fused updates issued once per launch group; *_alone are the same parts timed by themselves",
-                "ms": tp_ms["step"], "dx_gemm_alone_ms": tp_ms["dx_gemm"], "update_alone_ms": tp_ms["update"],
+                "ms": tp_ms.get("step"), "dx_gemm_alone_ms": tp_ms.get("dx_gemm"), "update_alone_ms": tp_ms.get("update"),
                 "reduce_scatter_alone_ms": tp_ms.get("reduce_scatter"), "reduce_scatters_per_step": n_rs if world > 1 else 0,
                 "ms_regather_x": tp_ms.get("step_regather_x"), "all_gather_x_alone_ms": tp_ms.get("all_gather_x"),
                 "ms_fused_dx_reduce_scatter": tp_ms.get("step_fused"),
@@ -728,6 +738,8 @@ def run_forge(args):
                 "dx_gemm": "forge_dgrad" if __import__("forge_b200.autograd", fromlist=["x"]).use_forge_dgrad else "cuBLAS",
                 "saved_activation_bytes_per_rank": {"gathered_x": act_full, "x_shards": act_full // world},
                 "steps": tp_steps, "launch": "cuda_graph" if not args.eager else "eager"}
+        if tp_errors:
+            line["tp_errors"] = tp_errors
         if parity is not None:
             line["tp_parity"] = "bit-equal" if not any(parity.values()) else f"{sum(parity.values())} differ"
             line["tp_parity_modes"] = parity
