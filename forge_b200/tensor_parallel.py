@@ -302,7 +302,10 @@ class RowShardedFusedLinear(nn.Module):
         """Use ``gather`` (a ``forge_b200.peer.GatheredLinear``), set ``index``, for this layer's forward:
         the all-gather of its input and of its output are fused into the GEMM.  The layer then takes the
         feature-sharded input and returns the FULL ``(…, V)`` output (``returns_full_output``), so the
-        caller must not gather it again.  Same conditions as ``attach_fused_scatter``."""
+        caller must not gather it again.  Same conditions as ``attach_fused_scatter``.  One training forward
+        per step and set (``GatheredLinear.begin_step`` between steps): the gathered input stays in the set's
+        buffer for the backward pass, so a second forward before it -- activation recomputation, two
+        micro-batches -- is refused rather than allowed to overwrite it."""
         self._gather, self._gather_index = gather, index
 
     def _fused_conditions(self, x) -> bool:
