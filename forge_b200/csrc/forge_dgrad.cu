@@ -479,8 +479,7 @@ int launch_dgrad(const ForgeDgradSegment* segs, int nseg, void* dX, int64_t BT, 
     if ((rc = encode_tmap_2d(&tm_out, dX, 2, true, BT, H, ld_dx, 64, 32, 128)) != FORGE_OK) return rc;
   }
   // CTA pairs (FORGE_DGRAD_PAIRS=1) when there is more than one 128-row tile to pair up.  Off by default:
-  // measured at BT = 512 they run at the rate of single CTAs (both forms are bound by the depth of the
-  // operand ring against the latency of the W stream, not by the bytes a stage moves).
+  // measured at BT = 512 they run at the rate of single CTAs, with seven or eight stages.
   static const bool pairs_allowed = [] {
     const char* e = getenv("FORGE_DGRAD_PAIRS");
     return e != nullptr && e[0] == '1';
