@@ -311,6 +311,10 @@ def run_forge(args):
     n_streams = max(1, args.streams)
     side_streams = [torch.cuda.Stream() for _ in range(n_streams - 1)]
     do_gather = world > 1 and args.gather_x
+    # End-to-end arm at N > 1: a rank's host inputs are what the row-sharded mode hands it between linears --
+    # its feature shard of X and its slice of dY; the full X is formed by the NCCL all-gather inside the
+    # timed step (uploading the full X on every rank would measure the host's memory system N times over).
+    e2e_gather = world > 1
     comm_stream = torch.cuda.Stream() if do_gather else None
 
     def step_device(step_no=None):
@@ -394,12 +398,12 @@ def run_forge(args):
                 name, V, H, grp, r0, r1, w, m, v = params[i]
                 dy_d = upload(dys[r1 - r0], ("dy", k), slot)
                 if grp not in x_by_grp:
-                    x_by_grp[grp] = upload(x_shard[H] if do_gather else x_full[H], ("x", len(x_by_grp)), slot)
+                    x_by_grp[grp] = upload(x_shard[H] if e2e_gather else x_full[H], ("x", len(x_by_grp)), slot)
                 staged_in.append((dy_d, x_by_grp[grp]))
             ready = torch.cuda.Event()
             ready.record(copy_stream)
             main.wait_event(ready)
-            gathered_x = {g: all_gather_features(t) for g, t in x_by_grp.items()} if do_gather else x_by_grp
+            gathered_x = {g: all_gather_features(t) for g, t in x_by_grp.items()} if e2e_gather else x_by_grp
             with K.UpdateGroup():
                 for (dy_d, _xd), i in zip(staged_in, members):
                     name, V, H, grp, r0, r1, w, m, v = params[i]
@@ -719,7 +723,10 @@ def run_forge(args):
                          "traffic": TRAFFIC_RATIO * alg / launches if (TRAFFIC_RATIO and args.moments == "bf16") else None,
                          "traffic_source": "ncu capture of one grouped decoder-layer launch (profiles/), scaled by algorithmic bytes"},
             "e2e": {"value": ms_e2e, "unit": "ms/step", "h2d_bytes_per_step": moved[0], "d2h_bytes_per_step": moved[1],
-                    "steps": e2e_steps},
+                    "steps": e2e_steps,
+                    "inputs": ("per rank: its feature shard of X and its rows' slice of dY from pinned host memory; "
+                               "X all-gathered by NCCL inside the step") if e2e_gather else
+                              "X and dY of every linear from pinned host memory"},
             "gpu_launches": launches * args.steps,
             "peak_hbm_gb": peak_gb, "device_status": status, "clocks": clocks,
         }
