@@ -18,13 +18,17 @@ preceding kernel has just produced them.
            timed steps on the launching stream, max over ranks).
 ``e2e``    the same step through the public operator API with HOST inputs: every launch first copies
            its X and dY from pinned host memory, and each step ends with a device-to-host read of a
-           status word and one updated weight.
+           status word and one updated weight.  At N > 1 a rank's host inputs are its feature shard of
+           X and its rows' slice of dY (what the row-sharded mode hands a rank between linears); the
+           full X is formed by the NCCL all-gather inside the timed step.
 N > 1      row-sharded tensor parallelism: rank r owns rows [r V/N, (r+1) V/N) of every weight and
            moment and updates them from its dY slice and the full X.  The path itself has no exchange
            step: the forward pass has already all-gathered X (it needs it for Y = X W^T) and autograd
            saved the gathered tensor, so the backward's fused update is purely local; strong scaling.
            ``--gather-x`` re-gathers X by NCCL inside the timed step (once per group of linears that
-           share it) for a design that saves the activation shards instead.
+           share it) for a design that saves the activation shards instead.  ``tp_step`` in the output
+           line times what the mode runs around the path (dX GEMM, reduce-scatter, updates), with
+           NCCL collectives and with the reduce-scatter fused into this library's dX GEMM.
 ``--impl reference``  the reference's own CPU-runnable path for this update -- torch autograd +
            ``torch.optim.AdamW`` on the host cores -- on a bounded sample (one decoder layer's seven
            projections), scaled to the full workload by parameter count.
